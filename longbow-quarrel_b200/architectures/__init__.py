@@ -1,1 +1,1 @@
-from . import fetorax, llama, zoporax  # noqa: F401  (registers LlamaForCausalLM, Fetorax and Zoporax)
+from . import fetorax, llama, raritar, zoporax  # noqa: F401  (registers LlamaForCausalLM, Fetorax, Raritar and Zoporax)

@@ -6,7 +6,8 @@ variant, blocks of 16 tokens behind a block table (internal/engine/kv_cache_page
 Here every sequence of a batch has its own length, so storage is a pool of pages of
 `page_size` tokens, [entry][page][kv_head][token][head_dim], and each slot has a row
 of page numbers.  A group whose layers attend to a window only gives pages back as
-they fall out of the window, so it holds a window's worth of pages per sequence.
+they fall out of the window, so it holds a window's worth of pages per sequence; with
+`keep_first`, the pages that hold a sequence's first positions stay with it as well.
 """
 from __future__ import annotations
 
@@ -22,10 +23,11 @@ NO_PAGE = -1
 class PagedKVGroup(CacheGroup):
     def __init__(self, entries: list[int], n_kv_heads: int, head_dim: int, window: int | None, n_pages: int,
                  page_size: int, max_slots: int, max_pages_per_seq: int, dtype: torch.dtype, device,
-                 v_head_dim: int | None = None, values: bool = True):
+                 v_head_dim: int | None = None, values: bool = True, keep_first: int = 0):
         self.entries = list(entries)
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.n_kv_heads, self.head_dim, self.window = n_kv_heads, head_dim, window
+        self.kept_pages = -(-int(keep_first) // page_size) if window is not None else 0    # pages that never go back early
         self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
         self.page_size, self.n_pages, self.max_pages_per_seq = page_size, n_pages, max_pages_per_seq
         shape = (len(self.entries), n_pages, n_kv_heads, page_size, head_dim)
@@ -94,7 +96,7 @@ class PagedKVGroup(CacheGroup):
             return
         keep_from = self.first_needed(length) // self.page_size
         row = self.table[slot]
-        for p in range(keep_from):
+        for p in range(self.kept_pages, keep_from):
             if row[p] != NO_PAGE:
                 self._free.append(int(row[p]))
                 row[p] = NO_PAGE

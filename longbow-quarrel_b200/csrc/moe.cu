@@ -2,10 +2,13 @@
 //
 //   lq_moe_route   router logits -> the chosen experts of every token and their weights
 //   lq_moe_up      u[t, j, :] = act(W_up[e(t, j)] h[t])             for the j-th chosen expert of token t
+//                  (gated: act(W_gate h) * (W_up h), the expert's gate rows stacked ahead of its up rows)
 //   lq_moe_down    y[t, :] = sum_j w(t, j) W_down[e(t, j)] u[t, j, :], in the order of j; optionally
 //                  + sigmoid(z_s[t]) * shared[t, :], and the whole added into the float32 stream
 //
-// Routing: scores s = sigmoid(z).  The experts form `groups` equal groups of neighbours; a group's score is the
+// Experts numbered n_real and above are identity experts: no matrices, their output is the weight times h[t] itself.
+//
+// Routing (the form the kernel started with; lq_moe_route's comment lists the others): scores s = sigmoid(z).  The experts form `groups` equal groups of neighbours; a group's score is the
 // sum of its two largest scores; only experts of the `keep` best groups can be chosen; of those the `top` with
 // the largest scores are (ties go to the lower index).  Weights: the chosen scores over their sum (+ 1e-20),
 // times `route_scale`.  Everything here is float32.
@@ -29,37 +32,56 @@ __device__ __forceinline__ int warp_argmax(const float* vals, int n, int lane) {
         const int oa = __shfl_xor_sync(0xffffffffu, at, o);
         if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
-    return at;
+    return at == 0x7fffffff ? 0 : at;
 }
 
+// score_fn 0: s = sigmoid(z); 1: s = softmax(z) over all E.  correction (optional, [E]): the choice is made by s + correction,
+// the weights by s alone.  group_rule 0: a group's score is the sum of its two largest choice scores; 1: its largest.
+// normalize: the chosen s over their sum (+ 1e-20); either way times route_scale.  Choice scores may be negative: what
+// cannot be chosen counts as minus infinity.
 __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const float* __restrict__ z, int z_stride, int* __restrict__ ids,
                                                                   float* __restrict__ weights, int T, int E, int groups, int keep,
-                                                                  int top, float route_scale) {
+                                                                  int top, float route_scale, int score_fn,
+                                                                  const float* __restrict__ correction, int group_rule,
+                                                                  int normalize) {
     pdl_launch_dependents();
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * MR_WARPS + warp;
-    float* score = sm + (size_t)warp * (2 * E + groups);      // [E] the scores
-    float* cand = score + E;                                  // [E] the scores still to be chosen from (-1: not)
+    float* score = sm + (size_t)warp * (3 * E + groups);      // [E] the scores
+    float* choice = score + E;                                // [E] the scores that the choice is made by
+    float* cand = choice + E;                                 // [E] the choice scores still to be chosen from (-inf: not)
     float* gs = cand + E;                                     // [groups]
     pdl_wait();
     if (t >= T) return;
     const int per = E / groups;
-    for (int e = lane; e < E; e += 32) score[e] = 1.f / (1.f + expf(-z[(size_t)t * z_stride + e]));
+    const float* zr = z + (size_t)t * z_stride;
+    if (score_fn == 1) {
+        float mx = -CUDART_INF_F;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zr[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float v = expf(zr[e] - mx); score[e] = v; sum += v; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
+    } else {
+        for (int e = lane; e < E; e += 32) score[e] = 1.f / (1.f + expf(-zr[e]));
+    }
+    for (int e = lane; e < E; e += 32) choice[e] = score[e] + (correction ? correction[e] : 0.f);
     __syncwarp();
     for (int g = lane; g < groups; g += 32) {
-        float a = -1.f, b = -1.f;                             // the two largest of the group
+        float a = -CUDART_INF_F, b = -CUDART_INF_F;           // the two largest of the group
         for (int i = 0; i < per; ++i) {
-            const float v = score[g * per + i];
+            const float v = choice[g * per + i];
             if (v > a) { b = a; a = v; } else if (v > b) b = v;
         }
-        gs[g] = a + (per > 1 ? b : 0.f);
+        gs[g] = a + ((group_rule == 0 && per > 1) ? b : 0.f);
     }
-    for (int e = lane; e < E; e += 32) cand[e] = -1.f;
+    for (int e = lane; e < E; e += 32) cand[e] = -CUDART_INF_F;
     __syncwarp();
     for (int n = 0; n < keep; ++n) {
         const int g = warp_argmax(gs, groups, lane);
         __syncwarp();
-        for (int i = lane; i < per; i += 32) cand[g * per + i] = score[g * per + i];
+        for (int i = lane; i < per; i += 32) cand[g * per + i] = choice[g * per + i];
         if (lane == 0) gs[g] = -CUDART_INF_F;
         __syncwarp();
     }
@@ -68,22 +90,23 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_route_kernel(const float* _
         const int e = warp_argmax(cand, E, lane);
         __syncwarp();
         sum += score[e];
-        if (lane == 0) { ids[(size_t)t * top + n] = e; cand[e] = -2.f; }
+        if (lane == 0) { ids[(size_t)t * top + n] = e; cand[e] = -CUDART_INF_F; }
         __syncwarp();
     }
-    const float inv = route_scale / (sum + 1e-20f);
-    for (int n = lane; n < top; n += 32) weights[(size_t)t * top + n] = score[ids[(size_t)t * top + n]] * inv;
+    const float mult = normalize ? route_scale / (sum + 1e-20f) : route_scale;
+    for (int n = lane; n < top; n += 32) weights[(size_t)t * top + n] = score[ids[(size_t)t * top + n]] * mult;
 }
 
 LQ_EXPORT int lq_moe_route(const float* z, int z_stride, int* ids, float* weights, int T, int E, int groups, int keep, int top,
-                           float route_scale, cudaStream_t stream) {
+                           float route_scale, int score_fn, const float* correction, int group_rule, int normalize,
+                           cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (E < 1 || groups < 1 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)) return LQ_BAD_SIZE;
-    const size_t smem = (size_t)MR_WARPS * (2 * E + groups) * sizeof(float);
+    const size_t smem = (size_t)MR_WARPS * (3 * E + groups) * sizeof(float);
     if (smem > 200 * 1024) return LQ_BAD_SIZE;
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_pdl(moe_route_kernel, dim3((T + MR_WARPS - 1) / MR_WARPS), dim3(MR_WARPS * 32), smem, stream, z, z_stride, ids,
-                      weights, T, E, groups, keep, top, route_scale);
+                      weights, T, E, groups, keep, top, route_scale, score_fn, correction, group_rule, normalize);
 }
 
 // act: 0 none, 1 gelu (erf), 2 gelu (tanh form), 3 silu, 4 relu
@@ -138,15 +161,16 @@ constexpr int MX_PER_WARP = 4;        // output rows a warp makes one after the 
 template <typename T>
 __global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up,
                                                                const int* __restrict__ ids, T* __restrict__ u, int top, int D,
-                                                               int F, int act) {
+                                                               int F, int act, int gated, int n_real) {
     pdl_launch_dependents();
     extern __shared__ __align__(16) float xs[];   // [D]
     const int pair = blockIdx.x, t = pair / top, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     for (int d = tid; d < D; d += MX_WARPS * 32) xs[d] = to_f32(h[(size_t)t * D + d]);
     const int e = ids[pair];
+    if (e >= n_real) return;                       // an identity expert has no matrices: its output is the input itself
     __syncthreads();
-    const T* w = w_up + (size_t)e * F * D;
+    const T* w = w_up + (size_t)e * (gated ? 2 : 1) * F * D;     // gated: F gate rows, then F up rows
     // The lanes' shares of all the warp's outputs first (their loads are in flight together), then the sums.
     float part[MX_PER_WARP];
 #pragma unroll
@@ -154,11 +178,19 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restri
         const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
         part[i] = f < F ? row_part(xs, w + (size_t)f * D, D, lane) : 0.f;
     }
+    float part_up[MX_PER_WARP];
+#pragma unroll
+    for (int i = 0; i < MX_PER_WARP; ++i) {
+        const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
+        part_up[i] = (gated && f < F) ? row_part(xs, w + (size_t)(F + f) * D, D, lane) : 0.f;
+    }
 #pragma unroll
     for (int i = 0; i < MX_PER_WARP; ++i) {
         const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
         const float s = warp_sum(part[i]);
-        if (lane == 0 && f < F) u[(size_t)pair * F + f] = from_f32<T>(moe_act(s, act));
+        const float up = gated ? warp_sum(part_up[i]) : 1.f;
+        // gated: the activated gate is rounded as a product's output would be before it meets the up value
+        if (lane == 0 && f < F) u[(size_t)pair * F + f] = from_f32<T>(gated ? moe_act(s, act) * up : moe_act(s, act));
     }
 }
 
@@ -168,14 +200,15 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
                                                                  const int* __restrict__ ids, const float* __restrict__ weights,
                                                                  const float* __restrict__ shared, const float* __restrict__ zs,
                                                                  int zs_stride, float* __restrict__ x, int accumulate, int top,
-                                                                 int D, int F) {
+                                                                 int D, int F, const T* __restrict__ h, int n_real,
+                                                                 float shared_scale) {
     pdl_launch_dependents();
     extern __shared__ __align__(16) float us[];   // [top][F]
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     for (int i = tid; i < top * F; i += MX_WARPS * 32) us[i] = to_f32(u[(size_t)t * top * F + i]);
     __syncthreads();
-    const float sg = (shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f;
+    const float sg = ((shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f) * shared_scale;
     float part[MX_PER_WARP];
 #pragma unroll
     for (int i = 0; i < MX_PER_WARP; ++i) {
@@ -183,6 +216,7 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
         part[i] = 0.f;
         if (d < D)
             for (int j = 0; j < top; ++j) {          // the choices in their order, weighted inside each lane's share
+                if (ids[(size_t)t * top + j] >= n_real) continue;
                 const T* wr = w_down + ((size_t)ids[(size_t)t * top + j] * D + d) * F;
                 part[i] = fmaf(weights[(size_t)t * top + j], row_part(us + j * F, wr, F, lane), part[i]);
             }
@@ -193,6 +227,8 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
         float y = warp_sum(part[i]);
         if (d >= D) continue;
         if (lane == 0) {
+            for (int j = 0; j < top; ++j)            // identity experts: the weight times the input itself
+                if (ids[(size_t)t * top + j] >= n_real) y = fmaf(weights[(size_t)t * top + j], to_f32(h[(size_t)t * D + d]), y);
             if (shared) y = fmaf(sg, shared[(size_t)t * D + d], y);
             float* o = x + (size_t)t * D + d;
             *o = accumulate ? *o + y : y;
@@ -201,14 +237,14 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
 }
 
 LQ_EXPORT int lq_moe_up(const void* h, const void* w_up, const int* ids, void* u, int dtype, int T, int top, int D, int F, int act,
-                        cudaStream_t stream) {
+                        int gated, int n_real, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (act < 0 || act > 4 || (size_t)D * 4 > 200 * 1024) return LQ_BAD_SIZE;
     dim3 grid(T * top, (F + MX_WARPS * MX_PER_WARP - 1) / (MX_WARPS * MX_PER_WARP));
     const size_t smem = (size_t)D * sizeof(float);
     typedef __nv_bfloat16 bf;
 #define LQ_GO(TT) do { if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        return launch_pdl(moe_up_kernel<TT>, grid, dim3(MX_WARPS * 32), smem, stream, (const TT*)h, (const TT*)w_up, ids, (TT*)u, top, D, F, act); } while (0)
+        return launch_pdl(moe_up_kernel<TT>, grid, dim3(MX_WARPS * 32), smem, stream, (const TT*)h, (const TT*)w_up, ids, (TT*)u, top, D, F, act, gated, n_real); } while (0)
     if (dtype == LQ_F32) LQ_GO(float);
     if (dtype == LQ_BF16) LQ_GO(bf);
 #undef LQ_GO
@@ -217,7 +253,7 @@ LQ_EXPORT int lq_moe_up(const void* h, const void* w_up, const int* ids, void* u
 
 LQ_EXPORT int lq_moe_down(const void* u, const void* w_down, const int* ids, const float* weights, const float* shared,
                           const float* zs, int zs_stride, float* x, int accumulate, int dtype, int T, int top, int D, int F,
-                          cudaStream_t stream) {
+                          const void* h, int n_real, float shared_scale, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     const size_t smem = (size_t)top * F * sizeof(float);
     if (smem > 200 * 1024) return LQ_BAD_SIZE;
@@ -225,7 +261,7 @@ LQ_EXPORT int lq_moe_down(const void* u, const void* w_down, const int* ids, con
     typedef __nv_bfloat16 bf;
 #define LQ_GO(TT) do { if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         return launch_pdl(moe_down_kernel<TT>, grid, dim3(MX_WARPS * 32), smem, stream, (const TT*)u, (const TT*)w_down, ids, weights, \
-                          shared, zs, zs_stride, x, accumulate, top, D, F); } while (0)
+                          shared, zs, zs_stride, x, accumulate, top, D, F, (const TT*)h, n_real, shared_scale); } while (0)
     if (dtype == LQ_F32) LQ_GO(float);
     if (dtype == LQ_BF16) LQ_GO(bf);
 #undef LQ_GO

@@ -42,6 +42,134 @@ LQ_EXPORT int lq_embedding(const void* table, int table_dtype, const int* tokens
     return lq_launch_status();
 }
 
+// Embedding of a token plus a row of a second table chosen by the pair (token before it, token):
+//   out[t] = table[tok] + pairs[(prev * mul_prev + tok * mul_cur) mod buckets],   pairs[buckets] at a sequence's first token.
+// The token before a step's first row is the sequence's state (last[slot], written by last_tokens_kernel after the
+// step's rows have been read); sums in float32.
+template <typename TW>
+__global__ void embedding_pairs_kernel(const TW* __restrict__ table, const TW* __restrict__ pairs, const int* __restrict__ tokens,
+                                       const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                       const int* __restrict__ slots, const int* __restrict__ cu_rows,
+                                       const int* __restrict__ last, float* __restrict__ out, int D, int V, int buckets,
+                                       long long mul_prev, long long mul_cur) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, b = tok_seq[t];
+    int tok = tokens[t];
+    if (tok < 0 || tok >= V) tok = 0;  // range is checked on the host before launch
+    long long at = buckets;
+    if (tok_pos[t] > 0) {
+        int prev = t > cu_rows[b] ? tokens[t - 1] : last[slots[b]];
+        if (prev < 0 || prev >= V) prev = 0;
+        at = (prev * mul_prev + tok * mul_cur) % buckets;
+        if (at < 0) at += buckets;
+    }
+    const TW* row = table + (size_t)tok * D;
+    const TW* pr = pairs + (size_t)at * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) out[(size_t)t * D + i] = to_f32(row[i]) + to_f32(pr[i]);
+}
+
+__global__ void last_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ cu_rows, const int* __restrict__ slots,
+                                   int* __restrict__ last, int B) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) last[slots[b]] = tokens[cu_rows[b + 1] - 1];
+}
+
+LQ_EXPORT int lq_embedding_pairs(const void* table, const void* pairs, int table_dtype, const int* tokens, const int* tok_pos,
+                                 const int* tok_seq, const int* slots, const int* cu_rows, int* last, float* out, int T, int B,
+                                 int D, int V, int buckets, long long mul_prev, long long mul_cur, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (buckets < 1) return LQ_BAD_SIZE;
+    int rc;
+    if (table_dtype == LQ_F32)
+        rc = launch_pdl(embedding_pairs_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)table, (const float*)pairs, tokens,
+                        tok_pos, tok_seq, slots, cu_rows, (const int*)last, out, D, V, buckets, mul_prev, mul_cur);
+    else if (table_dtype == LQ_BF16)
+        rc = launch_pdl(embedding_pairs_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)table,
+                        (const __nv_bfloat16*)pairs, tokens, tok_pos, tok_seq, slots, cu_rows, (const int*)last, out, D, V, buckets,
+                        mul_prev, mul_cur);
+    else
+        return LQ_BAD_DTYPE;
+    if (rc != LQ_OK) return rc;
+    return launch_pdl(last_tokens_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, tokens, cu_rows, slots, last, B);
+}
+
+// ------------------------------------------------------------------ short causal convolution over time, per channel
+//   out[t] = h[t] + sum_j w[:, j] * h[t - taps + 1 + j]      (j = 0 .. taps - 1; rows before the sequence's start are zero)
+// The taps - 1 rows ahead of a step's first row are the sequence's state [slot][taps - 1][D] (float32, oldest first,
+// zero when the sequence starts); conv_state_kernel moves it on once the step's rows have been read.  Sums in float32.
+template <typename T>
+__global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ h, T* __restrict__ out, const float* __restrict__ w,
+                                                          const float* __restrict__ state, const int* __restrict__ tok_seq,
+                                                          const int* __restrict__ slots, const int* __restrict__ cu_rows, int D,
+                                                          int taps, int add_input) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, b = tok_seq[t], first = cu_rows[b], i = t - first, keep = taps - 1;
+    const float* st = state + (size_t)slots[b] * keep * D;
+    for (int d = blockIdx.y * 256 + threadIdx.x; d < D; d += gridDim.y * 256) {
+        const float own = to_f32(h[(size_t)t * D + d]);
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int k = i - keep + j;        // the step's row that tap j reads; below 0: the state's row keep + k
+            const float v = j == keep ? own : (k >= 0 ? to_f32(h[(size_t)(first + k) * D + d]) : st[(size_t)(keep + k) * D + d]);
+            acc = fmaf(w[(size_t)d * taps + j], v, acc);
+        }
+        out[(size_t)t * D + d] = from_f32<T>(add_input ? own + acc : acc);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) conv_state_kernel(const T* __restrict__ h, float* __restrict__ state,
+                                                         const int* __restrict__ slots, const int* __restrict__ cu_rows, int D,
+                                                         int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x, first = cu_rows[b], n = cu_rows[b + 1] - first, keep = taps - 1;
+    float* st = state + (size_t)slots[b] * keep * D;
+    for (int d = blockIdx.y * 256 + threadIdx.x; d < D; d += gridDim.y * 256)
+        for (int k = 0; k < keep; ++k) {       // rising k: a row that moves down is read before it is overwritten
+            const int i = n - keep + k;
+            st[(size_t)k * D + d] = i >= 0 ? to_f32(h[(size_t)(first + i) * D + d]) : st[(size_t)(k + n) * D + d];
+        }
+}
+
+LQ_EXPORT int lq_causal_conv(const void* h, void* out, int dtype, const float* w, float* state, const int* tok_seq, const int* slots,
+                             const int* cu_rows, int T, int B, int D, int taps, int add_input, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (taps < 1 || (taps > 1 && !state)) return LQ_BAD_SIZE;
+    const int ny = (D + 1023) / 1024;
+    int rc;
+    typedef __nv_bfloat16 bf;
+    if (dtype == LQ_F32)
+        rc = launch_pdl(causal_conv_kernel<float>, dim3(T, ny), dim3(256), 0, stream, (const float*)h, (float*)out, w, (const float*)state,
+                        tok_seq, slots, cu_rows, D, taps, add_input);
+    else if (dtype == LQ_BF16)
+        rc = launch_pdl(causal_conv_kernel<bf>, dim3(T, ny), dim3(256), 0, stream, (const bf*)h, (bf*)out, w, (const float*)state, tok_seq,
+                        slots, cu_rows, D, taps, add_input);
+    else
+        return LQ_BAD_DTYPE;
+    if (rc != LQ_OK || taps == 1) return rc;
+    if (dtype == LQ_F32)
+        return launch_pdl(conv_state_kernel<float>, dim3(B, ny), dim3(256), 0, stream, (const float*)h, state, slots, cu_rows, D, taps);
+    return launch_pdl(conv_state_kernel<bf>, dim3(B, ny), dim3(256), 0, stream, (const bf*)h, state, slots, cu_rows, D, taps);
+}
+
+// ------------------------------------------------------------------ x += m * y (a branch that joins the stream with a multiplier)
+__global__ void add_scaled_kernel(float* __restrict__ x, const float* __restrict__ y, float m, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = fmaf(m, y[i], x[i]);
+}
+
+LQ_EXPORT int lq_add_scaled(float* x, const float* y, float m, long long total, cudaStream_t stream) {
+    if (total <= 0) return LQ_OK;
+    return launch_pdl(add_scaled_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, y, m, (size_t)total);
+}
+
 // ------------------------------------------------------------------ rmsnorm
 // x is the 32-bit residual stream.  rows (optional) picks the rows to normalise.
 template <typename TO>
@@ -430,7 +558,8 @@ LQ_EXPORT int lq_rope_kv_write(void* qkv, int dtype, const float* cos_t, const f
 // by the angle of its row's position (cos/sin tables [positions, rot/2]); the rest of the head passes.
 // Heads below k_first (the queries) go to qout [T, qout_stride], which may be buf itself; with a cache, heads
 // k_first.. go into the row's page of k_pages [page][Hkv][page_size][hd], and the values (with their bias)
-// into v_pages [..][vd].  The rows may be float32 while queries and cache are bfloat16: a product's 32-bit sums
+// into v_pages [..][vd] (with v_unit: each value head first divided by its root mean square, sqrt(mean(v^2) + v_eps)).
+// The rows may be float32 while queries and cache are bfloat16: a product's 32-bit sums
 // then meet their biases and angles before anything is rounded.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
@@ -438,7 +567,7 @@ rope_partial_kernel(const TI* buf, int stride, TO* qout, int qout_stride, const 
                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
                     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
                     const int* __restrict__ page_table, int pt_stride, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
-                    int n_rot, int k_first, int Hkv, int hd, int vd, int v_off, int page_size) {
+                    int n_rot, int k_first, int Hkv, int hd, int vd, int v_off, int page_size, int v_unit, float v_eps) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1;
@@ -471,7 +600,25 @@ rope_partial_kernel(const TI* buf, int stride, TO* qout, int qout_stride, const 
             if (kd) kd[d] = o;
         }
     }
-    if (v_pages) {
+    if (v_pages && v_unit) {
+        // Each value head divided by its root mean square (32-bit; eps inside the root): a warp per head.
+        const TI* vsrc = row + v_off;
+        const float* b = bias ? bias + v_off : nullptr;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int head = warp; head < Hkv; head += 8) {
+            float ss = 0.f;
+            for (int j = lane; j < vd; j += 32) {
+                const float v = to_f32(vsrc[head * vd + j]) + (b ? b[head * vd + j] : 0.f);
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+            const float inv = 1.f / sqrtf(ss / (float)vd + v_eps);
+            for (int j = lane; j < vd; j += 32) {
+                const float v = to_f32(vsrc[head * vd + j]) + (b ? b[head * vd + j] : 0.f);
+                v_pages[(at + (size_t)head * page_size) * vd + j] = from_f32<TO>(v * inv);
+            }
+        }
+    } else if (v_pages) {
         const TI* vsrc = row + v_off;
         const float* b = bias ? bias + v_off : nullptr;
         for (int i = threadIdx.x; i < Hkv * vd; i += 256) {
@@ -485,13 +632,13 @@ LQ_EXPORT int lq_rope_partial(const void* buf, int in_dtype, int stride, void* q
                               const float* bias, const float* cos_t, const float* sin_t, int rot, const int* tok_pos,
                               const int* tok_seq, const int* slots, const int* page_table, int pt_stride, void* k_pages,
                               void* v_pages, int T, int n_rot, int k_first, int Hkv, int hd, int vd, int v_off,
-                              int page_size, cudaStream_t stream) {
+                              int page_size, int v_unit, float v_eps, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (rot % 2 || rot > hd || (rot && (!cos_t || !sin_t)) || (!k_pages) != (!v_pages)) return LQ_BAD_SIZE;
     typedef __nv_bfloat16 bf;
 #define LQ_GO(TI, TO) return launch_pdl(rope_partial_kernel<TI, TO>, dim3(T), dim3(256), 0, stream, (const TI*)buf, stride, \
         (TO*)qout, qout_stride, bias, cos_t, sin_t, rot, tok_pos, tok_seq, slots, page_table, pt_stride, (TO*)k_pages, \
-        (TO*)v_pages, n_rot, k_first, Hkv, hd, vd, v_off, page_size)
+        (TO*)v_pages, n_rot, k_first, Hkv, hd, vd, v_off, page_size, v_unit, v_eps)
     if (in_dtype == LQ_F32 && out_dtype == LQ_F32) LQ_GO(float, float);
     if (in_dtype == LQ_BF16 && out_dtype == LQ_BF16) LQ_GO(bf, bf);
     if (in_dtype == LQ_F32 && out_dtype == LQ_BF16) LQ_GO(float, bf);
@@ -646,7 +793,8 @@ LQ_EXPORT int lq_softcap(float* x, long long total, float cap, cudaStream_t stre
 // read from its pages in chunks of ATT_CHUNK; the running maximum, sum and output
 // are carried from chunk to chunk, and inside a chunk every sum runs in key order.
 // The same kernel serves a prompt's tokens and a decoded token, so both reduce in the
-// same order.
+// same order.  cap > 0: score <- cap * tanh(score / cap) after the scale.  keep_first: with a window, the first
+// keep_first positions of the sequence stay visible (at their own positions) when the window has moved past them.
 constexpr int ATT_CHUNK = 128;
 
 template <typename T, typename TG>
@@ -656,7 +804,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ slots, T* __restrict__ out, int H, int Hkv, int hd,
                        int page_size, float scale, int window, int vd, const float* __restrict__ sink,
-                       const TG* __restrict__ gate, int gate_stride) {
+                       const TG* __restrict__ gate, int gate_stride, float cap, int keep_first) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float sm[];
@@ -674,17 +822,20 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
     float m = -CUDART_INF_F, l = 0.f;
     float acc0 = 0.f, acc1 = 0.f;  // output dims tid and tid + ATT_CHUNK (hd <= 256)
     const int* pt = page_table + (size_t)slot * pt_stride;
-    for (int base = start; base <= pos; base += ATT_CHUNK) {
-        int n = min(ATT_CHUNK, pos - base + 1);
+    // The keys a row sees: the first `head` positions that its window has left behind (keep_first), then its window.
+    const int head = min(keep_first, start), total = head + pos - start + 1;
+    for (int vbase = 0; vbase < total; vbase += ATT_CHUNK) {
+        int n = min(ATT_CHUNK, total - vbase);
         float s = -CUDART_INF_F;
         if (tid < n) {
-            int key = base + tid;
+            int key = vbase + tid < head ? vbase + tid : start + (vbase + tid - head);
             int page = pt[key / page_size];
             pg[tid] = page;
             const T* kr = k_pages + (((size_t)page * Hkv + kvh) * page_size + key % page_size) * hd;
             float d = 0.f;
             for (int i = 0; i < hd; ++i) d = fmaf(qs[i], to_f32(kr[i]), d);
             s = d * scale;
+            if (cap > 0.f) s = cap * tanhf(s / cap);
         }
         sc[tid] = s;
         __syncthreads();
@@ -702,7 +853,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
             if (d >= vd) break;
             float a = 0.f;
             for (int j = 0; j < n; ++j) {
-                int key = base + j;
+                int key = vbase + j < head ? vbase + j : start + (vbase + j - head);
                 const T* vr = v_pages + (((size_t)pg[j] * Hkv + kvh) * page_size + key % page_size) * vd;
                 a = fmaf(sc[j], to_f32(vr[d]), a);
             }
@@ -734,7 +885,7 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
                                  const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                  const int* slots, void* out, int T, int H, int Hkv, int hd, int page_size,
                                  float scale, int window, int vd, const float* sink, const void* gate, int gate_stride,
-                                 int gate_dtype, cudaStream_t stream) {
+                                 int gate_dtype, float cap, int keep_first, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (vd <= 0) vd = hd;
     if (vd > 2 * ATT_CHUNK || H % Hkv) return LQ_BAD_SIZE;
@@ -743,15 +894,15 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
     if (dtype == LQ_F32)
         return launch_pdl(attention_plain_kernel<float, float>, grid, dim3(ATT_CHUNK), smem, stream, (const float*)q, q_stride, (const float*)k_pages,
             (const float*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, (float*)out, H, Hkv, hd, page_size, scale, window,
-            vd, sink, (const float*)gate, gate_stride);
+            vd, sink, (const float*)gate, gate_stride, cap, keep_first);
     else if (dtype == LQ_BF16 && gate && gate_dtype == LQ_F32)
         return launch_pdl(attention_plain_kernel<__nv_bfloat16, float>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const float*)gate, gate_stride);
+            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const float*)gate, gate_stride, cap, keep_first);
     else if (dtype == LQ_BF16)
         return launch_pdl(attention_plain_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const __nv_bfloat16*)gate, gate_stride);
+            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const __nv_bfloat16*)gate, gate_stride, cap, keep_first);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();

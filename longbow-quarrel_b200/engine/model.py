@@ -15,7 +15,8 @@ class Model:
     def __init__(self, spec: ModelSpec, runtime: Runtime):
         self.spec, self.runtime = spec, runtime
         self.embedding = make_part("embedding", spec.embedding, runtime)
-        self.blocks = [make_part("block", PartSpec(layer.arrangement), runtime, layer=layer) for layer in spec.layers]
+        self.blocks = [make_part("block", PartSpec(layer.arrangement, dict(layer.params)), runtime, layer=layer)
+                       for layer in spec.layers]
         self.final_norm = make_part("norm", spec.final_norm, runtime)
         self.head = make_part("head", spec.head, runtime)
         self._order_known = False
@@ -32,6 +33,19 @@ class Model:
         for e in spec.schedule:
             if not e.writes_cache and e.cache not in writers:
                 raise ValueError(f"schedule: a run reads cache entry {e.cache}, which no run writes")
+        # State that parts keep for each sequence beside the mixers' cache entries (`state_need`: the embedding's, and
+        # every run of a block's own) gets cache entries of its own, numbered after the schedule's.
+        free = max([e.cache for e in spec.schedule], default=-1) + 1
+        self._state_entries: dict = {}
+        need = getattr(self.embedding, "state_need", lambda: None)()
+        if need is not None:
+            self._state_entries["embedding"] = (free, need)
+            free += 1
+        for n, entry in enumerate(spec.schedule):
+            need = getattr(self.blocks[entry.layer], "state_need", lambda: None)()
+            if need is not None:
+                self._state_entries[n] = (free, need)
+                free += 1
 
     # ------------------------------------------------------------------ weights
     def _named_parts(self):
@@ -72,7 +86,9 @@ class Model:
 
     def cache_needs(self) -> dict:
         """Cache entry -> what the mixer that writes it needs."""
-        return {e.cache: self.blocks[e.layer].cache_need() for e in self.spec.schedule if e.writes_cache}
+        needs = {e.cache: self.blocks[e.layer].cache_need() for e in self.spec.schedule if e.writes_cache}
+        needs.update({entry: need for entry, need in self._state_entries.values()})
+        return needs
 
     def step_needs(self) -> dict:
         """Name -> builder of every per-step integer array that some part asks for (see Part.step_needs)."""
@@ -107,7 +123,11 @@ class Model:
             self._order_known = True
             with linear.recording():
                 return self.forward(ctx, cache)
-        x = self.embedding.forward(ctx.tokens)
+        states = self._state_entries
+        if "embedding" in states:
+            x = self.embedding.forward(ctx.tokens, ctx=ctx, state=cache.view(states["embedding"][0]))
+        else:
+            x = self.embedding.forward(ctx.tokens)
         schedule = self.spec.schedule
         probe = self.probe
         if probe is not None:
@@ -115,6 +135,13 @@ class Model:
         normed = None           # rows of the next layer's first norm, when this layer's last product made them
         for i, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
+            if i in states:
+                # A block with state of its own (it folds no norms: what the layer ahead left unfinished is finished first).
+                block.forward(x, ctx, cache.view(entry.cache), entry.writes_cache, state=cache.view(states[i][0]))
+                normed = None
+                if probe is not None:
+                    probe(i, x, ctx)
+                continue
             if not getattr(block, "folds_norm", False):
                 block.forward(x, ctx, cache.view(entry.cache), entry.writes_cache)
                 normed = None

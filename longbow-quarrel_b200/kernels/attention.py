@@ -146,14 +146,15 @@ def _blocks(ctx, name):
     return tuple(flat.view(4, -1))
 
 
-def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None, vd=None, sink=None, gate=None):
+def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None, vd=None, sink=None, gate=None, softcap=None,
+              keep_first=0):
     """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*vd].  next_w: the weights the
     stream reads after the attention (the decode kernel asks for their first bytes as it ends).
     vd: size of a value head (default hd); sink: float32 [H], one more term of each head's softmax
     denominator; gate: [T, H*vd] whose sigmoid multiplies the output."""
     vd = vd or hd
-    if vd != hd:
-        return general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate)
+    if vd != hd or softcap or keep_first:
+        return general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate, softcap, keep_first)
     out = _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, gate)
     if gate is not None and out is not None:
         return ops.gate_mul(out, gate, "sigmoid")         # the tensor-core kernels leave the gate to a kernel of its own
@@ -196,8 +197,8 @@ def _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, ga
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, sink=sink)
 
 
-def general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate):
-    """Attention with a sink, a gate or values of another size than the keys."""
+def general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate, softcap=None, keep_first=0):
+    """Attention with a sink, a gate, values of another size than the keys, capped scores or kept first positions."""
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, vd=vd,
-                               sink=sink, gate=gate)
+                               sink=sink, gate=gate, softcap=softcap, keep_first=keep_first)

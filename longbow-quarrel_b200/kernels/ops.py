@@ -7,7 +7,7 @@ fallback: a tensor on the CPU, or a library that cannot be built, is an error.
 from __future__ import annotations
 
 import os
-from ctypes import c_float, c_int, c_long, c_void_p
+from ctypes import c_float, c_int, c_long, c_longlong, c_void_p
 
 import torch
 
@@ -161,6 +161,53 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor | Non
     return out
 
 
+def embedding_pairs(table: torch.Tensor, pairs: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int, tokens, tok_pos,
+                    tok_seq, slots, cu_rows, last: torch.Tensor, B: int) -> torch.Tensor:
+    """out[t] = table[tok_t] + pairs[(tok_(t-1) * mul_prev + tok_t * mul_cur) mod buckets] as float32; pairs[buckets] for a
+    sequence's first token.  `last` (int32 [slots]) holds each live sequence's last token between steps: read for a
+    step's first row, written with the step's last token afterwards."""
+    V, D = table.shape
+    T = tokens.numel()
+    if pairs.shape != (buckets + 1, D) or pairs.dtype != table.dtype or last.dtype != torch.int32:
+        raise KernelError(f"embedding_pairs: the second table must be [{buckets + 1}, {D}] of the first one's dtype, the state int32")
+    out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    fn = _fn("plain_kernels", "lq_embedding_pairs", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+                                                     c_void_p])
+    _check(fn(_p(_contig(table, "table")), _p(_contig(pairs, "pairs")), dtype_code(table), _p(tokens), _p(tok_pos), _p(tok_seq),
+              _p(slots), _p(cu_rows), _p(last), _p(out), T, B, D, V, int(buckets), int(mul_prev), int(mul_cur), _stream()),
+           "embedding_pairs", kernels=2)
+    return out
+
+
+def causal_conv(h: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, tok_seq, slots, cu_rows, B: int,
+                add_input: bool = True) -> torch.Tensor:
+    """out[t] = (h[t] +) sum_j w[:, j] h[t - taps + 1 + j] over each sequence's own rows, per channel; w float32 [D, taps].
+    state float32 [slots, taps - 1, D]: the rows ahead of a step's first row (zero at a sequence's start), moved on
+    by the step's rows afterwards."""
+    T, D = h.shape
+    taps = w.shape[1]
+    if w.dtype != torch.float32 or w.shape[0] != D or not w.is_contiguous():
+        raise KernelError("causal_conv: the taps must be contiguous float32 [D, taps]")
+    if taps > 1 and (state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps - 1, D) or not state.is_contiguous()):
+        raise KernelError(f"causal_conv: the state must be contiguous float32 [slots, {taps - 1}, {D}]")
+    out = torch.empty_like(h)
+    fn = _fn("plain_kernels", "lq_causal_conv", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(h, "h")), _p(out), dtype_code(h), _p(w), _p(state), _p(tok_seq), _p(slots), _p(cu_rows), T, B, D, taps,
+              int(add_input), _stream()), "causal_conv", kernels=2 if taps > 1 else 1)
+    return out
+
+
+def add_scaled(x: torch.Tensor, y: torch.Tensor, m: float) -> torch.Tensor:
+    """x += m * y, both float32 of one shape (a branch that joins the stream with a multiplier)."""
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or x.shape != y.shape or not x.is_contiguous() or not y.is_contiguous():
+        raise KernelError("add_scaled: two contiguous float32 tensors of one shape")
+    fn = _fn("plain_kernels", "lq_add_scaled", [c_void_p, c_void_p, c_float, c_longlong, c_void_p])
+    _check(fn(_p(x), _p(y), float(m), x.numel(), _stream()), "add_scaled")
+    return x
+
+
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype,
             rows: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """RMS norm of rows of the float32 stream x [T, D]; `rows` (int32) picks rows."""
@@ -234,9 +281,10 @@ def rope_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor
 def attention_plain(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int,
                     hd: int, page_size: int, scale: float, window: int | None,
                     out: torch.Tensor | None = None, vd: int | None = None, sink: torch.Tensor | None = None,
-                    gate: torch.Tensor | None = None) -> torch.Tensor:
+                    gate: torch.Tensor | None = None, softcap: float | None = None, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of every token over its own sequence's cache; q is the left
-    H*hd columns of a [T, q_stride] buffer.  vd: size of a value head (default hd).  sink: float32 [H], one
+    H*hd columns of a [T, q_stride] buffer.  softcap c: score <- c tanh(score / c) after the scale.  keep_first: with a
+    window, the sequence's first keep_first positions stay visible when the window has moved past them.  vd: size of a value head (default hd).  sink: float32 [H], one
     more term exp(sink) in each head's softmax denominator.  gate: a [T, H*vd] view (rows may be strided) whose
     sigmoid multiplies the output."""
     T = q.shape[0]
@@ -251,11 +299,12 @@ def attention_plain(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_
         out = torch.empty((T, H * vd), dtype=q.dtype, device=q.device)
     fn = _fn("plain_kernels", "lq_attention_plain", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                                     c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+                                                     c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+                                                     c_void_p])
     _check(fn(_p(q), q.stride(0), dtype_code(q), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0),
               _p(tok_pos), _p(tok_seq), _p(slots), _p(out), T, H, Hkv, hd, page_size, float(scale),
               int(window or 0), vd, _p(sink), _p(gate), gate.stride(0) if gate is not None else 0,
-              dtype_code(gate) if gate is not None else F32, _stream()), "attention")
+              dtype_code(gate) if gate is not None else F32, float(softcap or 0.0), int(keep_first or 0), _stream()), "attention")
     return out
 
 
@@ -319,12 +368,13 @@ def rmsnorm_add(y: torch.Tensor, gain: torch.Tensor, eps: float, x: torch.Tensor
 
 def rope_partial(buf: torch.Tensor, bias: torch.Tensor | None, cos, sin, rot: int, tok_pos, tok_seq, slots,
                  page_table, k_pages, v_pages, n_rot: int, k_first: int, Hkv: int, hd: int, vd: int, v_off: int,
-                 page_size: int, qout: torch.Tensor | None = None) -> None:
+                 page_size: int, qout: torch.Tensor | None = None, v_unit_eps: float | None = None) -> None:
     """Biases, then rotation of the first `rot` dimensions, for each of the n_rot heads at the left of buf's rows;
     heads below k_first (queries) go to `qout` [T, k_first * hd] (default: back in place), heads k_first.. into
     k_pages and the values at column v_off into v_pages where a cache is given.  bias: float32 over buf's
     columns, or None; cos/sin: float32 [positions, rot / 2].  buf may be float32 while qout and the cache are
-    bfloat16 (a product's 32-bit sums, rounded once, after bias and rotation)."""
+    bfloat16 (a product's 32-bit sums, rounded once, after bias and rotation).  v_unit_eps: each value head is divided by
+    its root mean square, sqrt(mean(v^2) + v_unit_eps), before it is stored."""
     T = buf.shape[0]
     if buf.stride(1) != 1:
         raise KernelError("rope_partial: rows must be contiguous")
@@ -342,11 +392,12 @@ def rope_partial(buf: torch.Tensor, bias: torch.Tensor | None, cos, sin, rot: in
         raise KernelError("rope_partial: the cache and the queries must have one dtype")
     fn = _fn("plain_kernels", "lq_rope_partial", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(_p(buf), dtype_code(buf), buf.stride(0), _p(qout), dtype_code(qout), qout.stride(0), _p(bias), _p(cos), _p(sin),
               int(rot), _p(tok_pos), _p(tok_seq), _p(slots), _p(page_table),
               page_table.stride(0) if page_table is not None else 0, _p(k_pages), _p(v_pages),
-              T, n_rot, k_first, Hkv, hd, vd, v_off, page_size, _stream()), "rope_partial")
+              T, n_rot, k_first, Hkv, hd, vd, v_off, page_size, int(v_unit_eps is not None), float(v_unit_eps or 0.0),
+              _stream()), "rope_partial")
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "gelu": 4}
@@ -626,38 +677,57 @@ def moe_combine(y: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, accumul
 MOE_ACTS = {None: 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "relu": 4}
 
 
-def moe_route(z: torch.Tensor, E: int, groups: int, keep: int, top: int, scale: float):
-    """Router logits z float32 [T, >= E] (the first E columns) -> (ids int32 [T, top], weights float32 [T, top]): sigmoid
-    scores; the `keep` best of `groups` equal groups of neighbouring experts by the sum of each group's two best scores;
-    of their experts the `top` best; weights = the chosen scores over their sum, times `scale`."""
+SCORE_FNS = {"sigmoid": 0, "softmax": 1}
+GROUP_RULES = {"top2": 0, "max": 1}
+
+
+def moe_route(z: torch.Tensor, E: int, groups: int, keep: int, top: int, scale: float, score: str = "sigmoid",
+              correction: torch.Tensor | None = None, group_rule: str = "top2", normalize: bool = True):
+    """Router logits z float32 [T, >= E] (the first E columns) -> (ids int32 [T, top], weights float32 [T, top]).
+    Scores s: sigmoid, or softmax over the E logits.  The choice is made by s + correction (float32 [E], optional):
+    the `keep` best of `groups` equal groups of neighbouring experts, a group scored by the sum of its two best
+    choice scores ("top2") or by its best ("max"); of their experts the `top` best.  weights = the chosen s (over
+    their sum with `normalize`) times `scale`."""
     T = z.shape[0]
     if z.dtype != torch.float32 or z.stride(1) != 1 or z.shape[1] < E:
         raise KernelError("moe_route: float32 logits with unit column stride")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E or not correction.is_contiguous()):
+        raise KernelError("moe_route: the correction must be contiguous float32 [E]")
     ids = torch.empty((T, top), dtype=torch.int32, device=z.device)
     weights = torch.empty((T, top), dtype=torch.float32, device=z.device)
-    fn = _fn("moe", "lq_moe_route", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
-    _check(fn(_p(z), z.stride(0), _p(ids), _p(weights), T, E, groups, keep, top, float(scale), _stream()), "moe_route")
+    fn = _fn("moe", "lq_moe_route", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                     c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_p(z), z.stride(0), _p(ids), _p(weights), T, E, groups, keep, top, float(scale), SCORE_FNS[score], _p(correction),
+              GROUP_RULES[group_rule], int(normalize), _stream()), "moe_route")
     return ids, weights
 
 
-def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: str | None) -> torch.Tensor:
-    """u[t, j] = act(w_up[ids[t, j]] h[t]) for w_up [E, F, D]; returns [T, top, F] in h's dtype."""
+def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: str | None, gated: bool = False) -> torch.Tensor:
+    """u[t, j] = act(w_up[ids[t, j]] h[t]) for w_up [E, F, D]; returns [T, top, F] in h's dtype.  gated: w_up is
+    [E, 2F, D], an expert's F gate rows ahead of its F up rows, and u = act(gate rows . h) * (up rows . h).  Chosen
+    experts numbered E and above (identity experts) have no rows; their u is left unwritten."""
     T, D = h.shape
     E, F, D2 = w_up.shape
+    if gated:
+        F //= 2
     if D2 != D or w_up.dtype != h.dtype or not w_up.is_contiguous():
         raise KernelError("moe_up: a contiguous weight [E, F, D] of the rows' dtype")
     top = ids.shape[1]
     u = torch.empty((T, top, F), dtype=h.dtype, device=h.device)
-    fn = _fn("moe", "lq_moe_up", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(_contig(h, "h")), _p(w_up), _p(ids), _p(u), dtype_code(h), T, top, D, F, MOE_ACTS[act], _stream()), "moe_up")
+    fn = _fn("moe", "lq_moe_up", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p])
+    _check(fn(_p(_contig(h, "h")), _p(w_up), _p(ids), _p(u), dtype_code(h), T, top, D, F, MOE_ACTS[act], int(gated), E, _stream()),
+           "moe_up")
     return u
 
 
 def moe_down(u: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor,
-             accumulate: bool = True, shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None) -> torch.Tensor:
-    """x[t] (+)= sum_j weights[t, j] w_down[ids[t, j]] u[t, j] (+ sigmoid(shared_gate[t]) * shared[t]) for w_down
-    [E, D, F]; x float32 [T, D]; shared float32 [T, D]; shared_gate float32 [T] (may be a strided column; None: the
-    shared rows are added as they are)."""
+             accumulate: bool = True, shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None,
+             h: torch.Tensor | None = None, shared_scale: float = 1.0) -> torch.Tensor:
+    """x[t] (+)= sum_j weights[t, j] w_down[ids[t, j]] u[t, j] (+ shared_scale * sigmoid(shared_gate[t]) * shared[t])
+    for w_down [E, D, F]; x float32 [T, D]; shared float32 [T, D]; shared_gate float32 [T] (may be a strided column;
+    None: the shared rows are added as they are).  h [T, D] (u's dtype): the experts' input, which a chosen expert
+    numbered E or above (an identity expert) passes on times its weight."""
     T, top, F = u.shape
     E, D, F2 = w_down.shape
     if F2 != F or w_down.dtype != u.dtype or not w_down.is_contiguous() or x.dtype != torch.float32 or tuple(x.shape) != (T, D):
@@ -666,11 +736,13 @@ def moe_down(u: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: 
         raise KernelError("moe_down: the shared rows must be contiguous float32 [T, D]")
     if shared_gate is not None and (shared_gate.dtype != torch.float32 or shared_gate.numel() != T):
         raise KernelError("moe_down: the shared gate must be float32 [T]")
+    if h is not None and (h.dtype != u.dtype or tuple(h.shape) != (T, D) or not h.is_contiguous()):
+        raise KernelError("moe_down: the experts' input must be contiguous [T, D] of u's dtype")
     fn = _fn("moe", "lq_moe_down", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                                    c_int, c_int, c_int, c_int, c_void_p])
+                                    c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p])
     _check(fn(_p(_contig(u, "u")), _p(w_down), _p(ids), _p(weights), _p(shared), _p(shared_gate),
               shared_gate.stride(0) if shared_gate is not None else 0, _p(_contig(x, "x")), int(accumulate), dtype_code(u),
-              T, top, D, F, _stream()), "moe_down")
+              T, top, D, F, _p(h), E if h is not None else (1 << 30), float(shared_scale), _stream()), "moe_down")
     return x
 
 

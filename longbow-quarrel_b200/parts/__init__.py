@@ -1,4 +1,4 @@
-from . import attention, block, dense_mlp, embedding, latent_attention, mlp, moe, norm, recurrent, rope  # noqa: F401  (registers the parts)
+from . import attention, block, conv, dense_mlp, embedding, latent_attention, mlp, moe, norm, recurrent, rope  # noqa: F401  (registers the parts)
 from .base import (CacheNeed, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, Runtime, StateNeed, StepContext)
 from .registry import make_part, register_part, registered_parts
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry

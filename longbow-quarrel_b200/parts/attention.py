@@ -18,7 +18,13 @@ number per head whose exponential is one more term of the softmax denominator, w
 no key and no value: p_j = exp(s_j) / (exp(sink) + sum exp(s_j'))); `gate` ("sigmoid":
 the heads' outputs times sigmoid(W_g h) before the output projection); and
 `own_kv=False` (the layer has no keys and values: it reads the cache entry that
-another layer writes, with its own queries).
+another layer writes, with its own queries); `softcap` c (score <- c tanh(score / c) after the
+scale); `keep_first` n (with a window, the first n positions of a sequence stay visible, at their own
+positions, when the window has moved past them); `value_norm_eps` (each value head is divided by its
+root mean square, sqrt(mean(v^2) + eps), before it is cached); a position part with interleaved pairs
+(the rows of the query and key projections are reordered at load, `parts.rope.pair_order`); and
+`cache_window` / `cache_keep_first`, what the cache entry keeps when layers that read it see further
+than the layer that writes it (default: the layer's own window and kept positions).
 """
 from __future__ import annotations
 
@@ -29,6 +35,7 @@ from ..kernels import linear, ops
 from ..weights.spec import WeightSpec
 from .base import KVNeed, Mixer, Runtime, StepContext
 from .registry import make_part, register_part
+from .rope import pair_order
 from .spec import PartSpec
 
 DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight"}
@@ -48,7 +55,9 @@ class Attention(Mixer):
     def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, position: PartSpec | None = None, window: int | None = None,
                  own_kv: bool = True, names: dict | None = None, value_dim: int | None = None, bias: bool = False,
-                 sink: bool = False, gate: str | None = None):
+                 sink: bool = False, gate: str | None = None, softcap: float | None = None, keep_first: int = 0,
+                 value_norm_eps: float | None = None, cache_window: int | None | str = "own",
+                 cache_keep_first: int | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if head_dim % 2 or not 2 <= head_dim <= 256:
@@ -64,6 +73,13 @@ class Attention(Mixer):
         if gate not in (None, "sigmoid"):
             raise ValueError(f"attention: gate {gate!r} is not supported (supported: 'sigmoid')")
         self.bias, self.sink, self.gate = bool(bias), bool(sink), gate
+        self.softcap = float(softcap) if softcap else None
+        self.keep_first = int(keep_first or 0) if window is not None else 0
+        self.value_norm_eps = None if value_norm_eps is None else float(value_norm_eps)
+        self.cache_window = window if cache_window == "own" else cache_window
+        self.cache_keep_first = self.keep_first if cache_keep_first is None else int(cache_keep_first)
+        if self.cache_window is not None and (window is None or window > self.cache_window or self.keep_first > self.cache_keep_first):
+            raise ValueError("attention: the cache entry must keep at least what the layer itself sees")
         self.names = {**DEFAULT_NAMES, **(names or {})}
         for key in ("q", "k", "v"):
             self.names.setdefault(key + "_bias", self.names[key].replace(".weight", "") + ".bias")
@@ -74,13 +90,15 @@ class Attention(Mixer):
         # The kernels that fuse rotation and cache write into the projections, and the tensor-core attention
         # kernels, know the plain form only; every option above takes the general kernels.
         self.general = self.bias or self.sink or self.gate is not None or self.vd != head_dim or \
-            (self.position is not None and self.rot != head_dim)
+            (self.position is not None and self.rot != head_dim) or self.softcap is not None or self.keep_first > 0 or \
+            self.value_norm_eps is not None
         self.b_qkv = self.sinks = None
         self.w_qkv: linear.LinearWeight | None = None
         self.w_o: linear.LinearWeight | None = None
 
     def cache_need(self):
-        return KVNeed(self.Hkv, self.hd, self.window, self.vd if self.vd != self.hd else None)
+        return KVNeed(self.Hkv, self.hd, self.cache_window, self.vd if self.vd != self.hd else None,
+                      keep_first=self.cache_keep_first if self.cache_window is not None else 0)
 
     def step_needs(self):
         return attention_kernels.step_needs(self.runtime.act_dtype, self.hd, self.H, self.Hkv, self.window,
@@ -105,8 +123,21 @@ class Attention(Mixer):
             out.update(self.position.weights())        # a position encoding may have tensors of its own
         return out
 
+    def _reordered(self, w: torch.Tensor, heads: int) -> torch.Tensor:
+        """Rows (or entries) of a query or key projection in the order in which the kernels' half-split pairs are
+        the position part's interleaved ones."""
+        if not getattr(self.position, "interleaved", False):
+            return w
+        order = torch.tensor(pair_order(self.hd, self.rot), device=w.device)
+        return w.reshape(heads, self.hd, *w.shape[1:])[:, order].reshape(w.shape).contiguous()
+
     def load(self, tensors):
         n = self.names
+        tensors = dict(tensors)
+        for key, heads in (("q", self.H), ("k", self.Hkv)):
+            for name in (n[key], n[key + "_bias"]):
+                if name in tensors and (key == "q" or self.own_kv):
+                    tensors[name] = self._reordered(tensors[name], heads)
         rows = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
         if self.gate is not None:
             rows.append(tensors[n["g"]])               # the gate's rows ride in the same product, after q, k and v
@@ -141,11 +172,12 @@ class Attention(Mixer):
         ops.rope_partial(rows, self.b_qkv, cos, sin, self.rot if tables is not None else 0, ctx.tok_pos, ctx.tok_seq,
                          ctx.slots, cache_view.page_table if store else None, cache_view.k_pages if store else None,
                          cache_view.v_pages if store else None, H + (G if self.own_kv else 0), H, G, hd, vd, v_off,
-                         cache_view.page_size, qout=q if wide else None)
+                         cache_view.page_size, qout=q if wide else None, v_unit_eps=self.value_norm_eps)
         g_off = H * hd + (G * (hd + vd) if self.own_kv else 0)
         gate = rows[:, g_off:g_off + H * vd] if self.gate is not None else None
         out = attention_kernels.attention(q, cache_view, ctx, H, G, hd, self.scale, self.window,
-                                          next_w=self.w_o.tensor, vd=vd, sink=self.sinks, gate=gate)
+                                          next_w=self.w_o.tensor, vd=vd, sink=self.sinks, gate=gate, softcap=self.softcap,
+                                          keep_first=self.keep_first)
         return self._project(out, residual, None)
 
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True, emit=None):

@@ -126,12 +126,13 @@ class KVNeed(CacheNeed):
     window: int | None = None
     v_head_dim: int | None = None        # values of another size than the keys
     values: bool = True                  # False: no pool of values (a mixer whose values are a part of its keys' rows)
+    keep_first: int = 0                  # with a window: the sequence's first positions that stay readable for good
 
     def make_group(self, entries, sizing):
         from ..cache.paged import PagedKVGroup
         return PagedKVGroup(entries, self.n_kv_heads, self.head_dim, self.window, sizing.n_pages, sizing.page_size,
                             sizing.max_slots, sizing.pages_per_seq, sizing.dtype, sizing.device,
-                            v_head_dim=self.v_head_dim, values=self.values)
+                            v_head_dim=self.v_head_dim, values=self.values, keep_first=self.keep_first)
 
 
 @dataclass(frozen=True)

@@ -5,6 +5,11 @@ alone), the order of the reference's
 block (internal/device/metal.go:1347-1527), with the residual stream x in 32-bit
 throughout (internal/engine/engine.go:1375).
 
+Two options of "pre_norm" that other designs use: a part in the place `conv1` (role "conv": a short causal
+convolution over time) filters what the mixer reads, h <- conv1(norm1(x)), with the rows it needs from earlier
+steps kept as the layer's own state; and `residual_scale` m, x += m * mixer(...), x += m * ffn(...), for which
+the mixer and the feed-forward hand back their branches as float32 rows.
+
 "sandwich_norm": every branch is normed on both sides, x += norm1b(mixer(norm1(x)));
 x += norm2b(ffn(norm2(x))), and a layer may have no feed-forward.  The branch's own norm,
 the addition and the norm that reads the stream next are one kernel."""
@@ -18,25 +23,37 @@ from .spec import LayerSpec
 
 @register_part("block", "pre_norm")
 class PreNormBlock(Part):
-    def __init__(self, runtime: Runtime, layer: LayerSpec):
+    def __init__(self, runtime: Runtime, layer: LayerSpec, residual_scale: float = 1.0):
         self.prefix = layer.prefix
-        unknown = set(layer.parts) - {"norm1", "mixer", "norm2", "ffn"}
+        unknown = set(layer.parts) - {"norm1", "conv1", "mixer", "norm2", "ffn"}
         if unknown:
             raise ValueError(f"layer {layer.prefix!r}: the arrangement 'pre_norm' has no place {sorted(unknown)}")
         if len(set(layer.parts) & {"norm2", "ffn"}) == 1:
             raise ValueError(f"layer {layer.prefix!r}: norm2 and ffn come together or not at all")
         self.norm1 = make_part("norm", layer.part("norm1"), runtime)
+        self.conv1 = make_part("conv", layer.part("conv1"), runtime) if "conv1" in layer.parts else None
         self.mixer = make_part("mixer", layer.part("mixer"), runtime)
         self.has_ffn = "ffn" in layer.parts
         self.norm2 = make_part("norm", layer.part("norm2"), runtime) if self.has_ffn else None
         self.ffn = make_part("ffn", layer.part("ffn"), runtime) if self.has_ffn else None
+        self.scale = float(residual_scale)
+        if self.scale != 1.0 and not getattr(self.mixer, "returns_branch", False):
+            raise ValueError(f"layer {layer.prefix!r}: the mixer {layer.part('mixer').kind!r} cannot hand back its output "
+                             f"for a multiplier on the branch")
+        # The products that fold norms add their output straight into the stream and read the norm's unfinished rows:
+        # neither goes with a multiplier on the branch or with a filter between the norm and the mixer.
+        self.folds_norm = self.scale == 1.0 and self.conv1 is None
 
     def parts(self):
-        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None)
+        return tuple(p for p in (self.norm1, self.conv1, self.mixer, self.norm2, self.ffn) if p is not None)
 
     def cache_need(self):
         """What the layer's cache entry must hold: its mixer's need."""
         return self.mixer.cache_need()
+
+    def state_need(self):
+        """What every run of the layer keeps for each sequence beside its mixer's cache entry: the filter's rows."""
+        return self.conv1.state_need() if self.conv1 is not None else None
 
     def step_needs(self):
         out = {}
@@ -61,16 +78,36 @@ class PreNormBlock(Part):
         for part in self.parts():
             part.load({n: tensors[n] for n in part.weights()})
 
-    folds_norm = True
-
     def input_norm(self, n_rows: int):
         """(gain, eps) when the layer ahead of this one may leave this layer's first norm to the
         products on either side of it; None otherwise."""
         return self.norm1.foldable(n_rows) if self.mixer.folds_norm else None
 
-    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool = True, normed=None, emit=None):
+    def _forward_plain(self, x, ctx: StepContext, cache_view, writes_cache: bool, state):
+        """The layer with a filter ahead of its mixer or a multiplier on its branches: every norm a kernel of its own."""
+        h = self.norm1.forward(x)
+        if self.conv1 is not None:
+            h = self.conv1.forward(h, ctx, state)
+        if self.scale == 1.0:
+            self.mixer.forward(h, ctx, cache_view, x, writes_cache)
+        else:
+            ops.add_scaled(x, self.mixer.forward(h, ctx, cache_view, None, writes_cache), self.scale)
+        if self.has_ffn:
+            h = self.norm2.forward(x)
+            if self.scale == 1.0:
+                self.ffn.forward(h, ctx, x)
+            elif getattr(self.ffn, "takes_scale", False):
+                self.ffn.forward(h, ctx, x, scale=self.scale)          # the feed-forward's last kernel multiplies as it adds
+            else:
+                ops.add_scaled(x, self.ffn.forward(h, ctx, None), self.scale)
+        return None
+
+    def forward(self, x, ctx: StepContext, cache_view, writes_cache: bool = True, normed=None, emit=None, state=None):
         """`normed`: the rows of norm1, when the layer ahead made them (see input_norm).  `emit`: the
-        input_norm() of the layer that follows.  Returns that layer's rows, or None."""
+        input_norm() of the layer that follows.  `state`: the view of what `state_need` asked for.  Returns the
+        next layer's rows, or None."""
+        if not self.folds_norm:
+            return self._forward_plain(x, ctx, cache_view, writes_cache, state)
         n_rows = x.shape[0]
         h = normed if normed is not None else self.norm1.forward(x)
         if not self.has_ffn:

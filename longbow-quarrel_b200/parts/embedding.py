@@ -12,7 +12,7 @@ import torch
 
 from ..kernels import linear, ops
 from ..weights.spec import WeightSpec
-from .base import Part, Runtime
+from .base import Part, Runtime, StateNeed
 from .registry import register_part
 
 
@@ -32,6 +32,45 @@ class TokenEmbedding(Part):
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         return ops.embedding(self.table, tokens)
+
+
+@register_part("embedding", "pair_hash_embedding")
+class PairHashEmbedding(Part):
+    """Token embedding plus a row of a second table chosen by the pair (token before, token):
+
+        x_t = table[tok_t] + pairs[(tok_(t-1) * mul_prev + tok_t * mul_cur) mod buckets]
+
+    and `pairs[buckets]`, the table's last row, for the first token of a sequence.  The token before a step's first
+    row is part of the sequence's state: one int32 per slot (`state_need`), which the step's last token replaces."""
+
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str, pairs_name: str, buckets: int,
+                 mul_prev: int, mul_cur: int):
+        if buckets < 1:
+            raise ValueError(f"pair_hash_embedding: {buckets} buckets")
+        self.runtime, self.vocab_size, self.hidden_size = runtime, vocab_size, hidden_size
+        self.name, self.pairs_name = name, pairs_name
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.table: torch.Tensor | None = None
+        self.pairs: torch.Tensor | None = None
+
+    def weights(self):
+        return {self.name: WeightSpec((self.vocab_size, self.hidden_size)),
+                self.pairs_name: WeightSpec((self.buckets + 1, self.hidden_size))}
+
+    def load(self, tensors):
+        self.table, self.pairs = tensors[self.name], tensors[self.pairs_name]
+        if self.pairs.dtype != self.table.dtype:
+            self.table, self.pairs = self.table.to(torch.float32), self.pairs.to(torch.float32)
+
+    def state_need(self):
+        """The sequence's last token, kept between steps."""
+        return StateNeed((), torch.int32)
+
+    def forward(self, tokens: torch.Tensor, ctx=None, state=None) -> torch.Tensor:
+        return ops.embedding_pairs(self.table, self.pairs, self.buckets, self.mul_prev, self.mul_cur, tokens, ctx.tok_pos,
+                                   ctx.tok_seq, ctx.slots, ctx.cu_rows, state, ctx.B)
 
 
 @register_part("head", "linear_head")

@@ -64,6 +64,13 @@ class GatedMLP(FeedForward):
             self.b_down = tensors[n["down_bias"]].to(torch.float32).contiguous()
 
     def forward(self, h, ctx: StepContext, residual, emit=None):
+        """With `residual` None the output comes back as float32 [T, D] instead of being added."""
+        if residual is None:
+            if self.plain:
+                return linear.linear(linear.linear_swiglu(h, self.w_gu, self.block), self.w_down, torch.float32)
+            gu = linear.linear(h, self.w_gu, torch.float32 if self.bias else self.runtime.act_dtype)
+            out = linear.linear(ops.gated_act(gu, self.b_gu, self.activation, self.runtime.act_dtype), self.w_down, torch.float32)
+            return ops.add_bias(out, self.b_down) if self.bias else out
         if not self.plain:
             # Biases meet the product's 32-bit sums before anything is rounded.
             gu = linear.linear(h, self.w_gu, torch.float32 if self.bias else self.runtime.act_dtype)

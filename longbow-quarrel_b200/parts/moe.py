@@ -7,7 +7,15 @@
     y = sum_e g_e W_down,e act(W_up,e h)  [ + sigmoid(w_sg . h) * shared(h) ]
 
 The experts have no gate and no bias.  A shared expert (a `dense_mlp` of its own size) runs for every
-token behind one sigmoid number per token.  The router's logits and the shared expert's gate come
+token behind one sigmoid number per token.
+
+Options that other designs use, each a parameter: `score` "softmax" (over all router outputs) instead of "sigmoid";
+`correction` (a tensor of one number per router output that is added to the scores for the choice only: groups and
+experts are chosen by s + correction, the weights are the plain s); `group_rule` "max" (a group's score is its best
+choice score) instead of "top2"; `normalize` False (the weights are the chosen scores as they are); `gated` (an expert
+is W_down (act(W_gate h) * (W_up h)), and so is the shared expert); `identity` n (the router has n more outputs than
+there are experts; a token that chooses one of those gets its own input h back, times the weight; they have no tensors,
+and groups are formed over experts and identity outputs together).  The router's logits and the shared expert's gate come
 from one 32-bit product; choice and weights are one kernel.  Few tokens (a decode step): the experts' two
 products are one kernel each that streams every token's own experts (`csrc/moe.cu`), the second of which also
 adds the shared expert's rows and joins the stream.  Many tokens (a prompt, bfloat16): the (token, choice) pairs
@@ -40,31 +48,52 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, runtime: Runtime, hidden_size: int, n_experts: int, top: int, expert_size: int,
                  activation: str = "gelu", groups: int = 1, keep_groups: int = 1, route_scale: float = 1.0,
-                 shared_size: int | None = None, shared_activation: str | None = None, names: dict | None = None):
+                 shared_size: int | None = None, shared_activation: str | None = None, names: dict | None = None,
+                 score: str = "sigmoid", correction: bool = False, group_rule: str = "top2", normalize: bool = True,
+                 gated: bool = False, identity: int = 0):
         if activation not in ops.MOE_ACTS:
             raise ValueError(f"routed_experts: activation {activation!r} is not one of {', '.join(map(str, ops.MOE_ACTS))}")
-        if n_experts % groups or not 1 <= keep_groups <= groups:
-            raise ValueError(f"routed_experts: {n_experts} experts in {groups} groups, {keep_groups} kept")
-        if not 1 <= top <= keep_groups * (n_experts // groups):
-            raise ValueError(f"routed_experts: {top} experts per token, but only {keep_groups * (n_experts // groups)} can be chosen")
+        if score not in ops.SCORE_FNS or group_rule not in ops.GROUP_RULES:
+            raise ValueError(f"routed_experts: score {score!r} / group rule {group_rule!r} (scores: {', '.join(ops.SCORE_FNS)}; "
+                             f"group rules: {', '.join(ops.GROUP_RULES)})")
+        routed = n_experts + int(identity)              # what the router chooses from
+        if identity < 0 or routed % groups or not 1 <= keep_groups <= groups:
+            raise ValueError(f"routed_experts: {n_experts} experts and {identity} identity outputs in {groups} groups, {keep_groups} kept")
+        if not 1 <= top <= keep_groups * (routed // groups):
+            raise ValueError(f"routed_experts: {top} experts per token, but only {keep_groups * (routed // groups)} can be chosen")
         self.runtime, self.D, self.E, self.top, self.F = runtime, hidden_size, n_experts, top, expert_size
+        self.routed, self.identity = routed, int(identity)
         self.activation, self.groups, self.keep, self.route_scale = activation, groups, keep_groups, float(route_scale)
-        self.names = {"router": "router", "expert": "e{}", "up": "up", "down": "down", "shared": "shared", "shared_gate": "shared.sg",
-                      **(names or {})}
+        self.score, self.has_correction, self.group_rule, self.normalize = score, bool(correction), group_rule, bool(normalize)
+        self.gated = bool(gated)
+        self.names = {"router": "router", "expert": "e{}", "gate": "gate", "up": "up", "down": "down", "shared": "shared",
+                      "shared_gate": "shared.sg", "correction": "correction", **(names or {})}
         self.shared = None
         if shared_size:
             n = self.names
-            self.shared = make_part("ffn", PartSpec("dense_mlp", {
-                "hidden_size": hidden_size, "intermediate_size": shared_size, "activation": shared_activation or activation,
-                "names": {"up": f"{n['shared']}.{n['up']}", "down": f"{n['shared']}.{n['down']}"}}), runtime)
-        self.w_route = self.w_up = self.w_down = None
+            if self.gated:
+                self.shared = make_part("ffn", PartSpec("gated_mlp", {
+                    "hidden_size": hidden_size, "intermediate_size": shared_size, "activation": shared_activation or activation,
+                    "names": {"gate": f"{n['shared']}.{n['gate']}", "up": f"{n['shared']}.{n['up']}",
+                              "down": f"{n['shared']}.{n['down']}"}}), runtime)
+            else:
+                self.shared = make_part("ffn", PartSpec("dense_mlp", {
+                    "hidden_size": hidden_size, "intermediate_size": shared_size, "activation": shared_activation or activation,
+                    "names": {"up": f"{n['shared']}.{n['up']}", "down": f"{n['shared']}.{n['down']}"}}), runtime)
+        self.w_route = self.w_up = self.w_down = self.correction = None
+
+    takes_scale = True        # forward(..., scale=m): the whole output times m as it joins the stream
 
     def _expert(self, e: int, which: str) -> str:
         return f"{self.names['expert'].format(e)}.{self.names[which]}"
 
     def weights(self):
-        out = {self.names["router"]: WeightSpec((self.E, self.D))}
+        out = {self.names["router"]: WeightSpec((self.routed, self.D))}
+        if self.has_correction:
+            out[self.names["correction"]] = WeightSpec((self.routed,), init="small", full_precision=True)
         for e in range(self.E):
+            if self.gated:
+                out[self._expert(e, "gate")] = WeightSpec((self.F, self.D))
             out[self._expert(e, "up")] = WeightSpec((self.F, self.D))
             out[self._expert(e, "down")] = WeightSpec((self.D, self.F))
         if self.shared is not None:
@@ -75,7 +104,13 @@ class RoutedExperts(FeedForward):
     def load(self, tensors):
         rows = [tensors[self.names["router"]]] + ([tensors[self.names["shared_gate"]]] if self.shared is not None else [])
         self.w_route = torch.cat(rows, dim=0).contiguous()           # the shared expert's gate rides behind the router's rows
-        self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous()
+        if self.has_correction:
+            self.correction = tensors[self.names["correction"]].to(torch.float32).contiguous()
+        if self.gated:          # an expert's gate rows ahead of its up rows: one stream of [2F, D] per expert
+            self.w_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]])
+                                     for e in range(self.E)]).contiguous()
+        else:
+            self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.E)]).contiguous()
         if self.w_up.dtype != self.runtime.act_dtype:
             # The experts' kernels read rows and weights of one dtype.
@@ -83,13 +118,16 @@ class RoutedExperts(FeedForward):
         if self.shared is not None:
             self.shared.load({name: tensors[name] for name in self.shared.weights()})
 
-    def forward(self, h, ctx: StepContext, residual):
-        z = ops.small_proj(h, self.w_route)                          # float32 [T, E (+ 1)]
-        ids, weights = ops.moe_route(z, self.E, self.groups, self.keep, self.top, self.route_scale)
+    def forward(self, h, ctx: StepContext, residual, scale: float = 1.0):
+        """scale: a multiplier on the whole output (the chosen experts' weights and the shared expert's gate carry it)."""
+        z = ops.small_proj(h, self.w_route)                          # float32 [T, routed (+ 1)]
+        ids, weights = ops.moe_route(z, self.routed, self.groups, self.keep, self.top, self.route_scale * scale, score=self.score,
+                                     correction=self.correction, group_rule=self.group_rule, normalize=self.normalize)
         shared = self.shared.forward(h, ctx, None) if self.shared is not None else None
-        gate = z[:, self.E] if self.shared is not None else None
+        gate = z[:, self.routed] if self.shared is not None else None
         T = h.shape[0]
-        if T * self.top >= self.TILED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
+        plain = not self.gated and not self.identity and scale == 1.0      # the form that the grouped products know
+        if plain and T * self.top >= self.TILED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
             # A prompt: the pairs in the order of their experts, every expert padded to whole row tiles, so that each
             # tile of the tcgen05 product reads one expert's weight; the second product reads the first one's rows as
             # they lie, and the combination finds each pair's row through the order's inverse.
@@ -101,7 +139,7 @@ class RoutedExperts(FeedForward):
             out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
             ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate, place=dst)
             return None if residual is not None else out
-        if T * self.top >= self.GROUPED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
+        if plain and T * self.top >= self.GROUPED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
             # Many tokens: the pairs sorted by expert (on the device), each expert's rows as tiles of a tensor-core product.
             listed = ops.group_rows(ids.view(-1), self.E)
             u = torch.empty((T * self.top, self.F), dtype=h.dtype, device=h.device)
@@ -111,9 +149,10 @@ class RoutedExperts(FeedForward):
             out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
             ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate)
             return None if residual is not None else out
-        u = ops.moe_up(h, self.w_up, ids, self.activation)
+        u = ops.moe_up(h, self.w_up, ids, self.activation, gated=self.gated)
+        more = dict(h=h if self.identity else None, shared_scale=scale)
         if residual is None:
             out = torch.empty((h.shape[0], self.D), dtype=torch.float32, device=h.device)
-            return ops.moe_down(u, self.w_down, ids, weights, out, accumulate=False, shared=shared, shared_gate=gate)
-        ops.moe_down(u, self.w_down, ids, weights, residual, accumulate=True, shared=shared, shared_gate=gate)
+            return ops.moe_down(u, self.w_down, ids, weights, out, accumulate=False, shared=shared, shared_gate=gate, **more)
+        ops.moe_down(u, self.w_down, ids, weights, residual, accumulate=True, shared=shared, shared_gate=gate, **more)
         return None

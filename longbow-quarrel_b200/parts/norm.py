@@ -15,17 +15,23 @@ from .registry import register_part
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, runtime: Runtime, size: int, eps: float, name: str = "weight", offset: float = 0.0):
+    def __init__(self, runtime: Runtime, size: int, eps: float, name: str = "weight", offset: float = 0.0,
+                 scalar: bool = False):
         """offset: what is added to the stored tensor to give the gain (1 for checkpoints that keep their
-        gains minus one: y = x / rms(x) * (1 + w)); the sum is made once, in 32-bit, when the tensor is loaded."""
+        gains minus one: y = x / rms(x) * (1 + w)); the sum is made once, in 32-bit, when the tensor is loaded.
+        scalar: the stored gain is one number (a tensor without dimensions) that serves every coordinate."""
         self.runtime, self.size, self.eps, self.name, self.offset = runtime, size, float(eps), name, float(offset)
+        self.scalar = bool(scalar)
         self.gain: torch.Tensor | None = None
 
     def weights(self):
-        return {self.name: WeightSpec((self.size,), init="gain" if self.offset == 0.0 else "small", full_precision=True)}
+        shape = () if self.scalar else (self.size,)
+        return {self.name: WeightSpec(shape, init="gain" if self.offset == 0.0 else "small", full_precision=True)}
 
     def load(self, tensors):
-        self.gain = (tensors[self.name].to(torch.float32) + self.offset).contiguous()
+        gain = tensors[self.name].to(torch.float32) + self.offset
+        # One number for all coordinates is kept as a row of equal gains: every kernel that reads gains takes it as it is.
+        self.gain = (gain.reshape(1).expand(self.size) if self.scalar else gain).contiguous()
 
     def forward(self, x, rows=None):
         return ops.rmsnorm(x, self.gain, self.eps, self.runtime.act_dtype, rows)

@@ -1,11 +1,11 @@
 """The registry of parts: role ("mixer", "ffn", "norm", "position", "embedding",
-"head", "block") and kind -> class.  A new kind of part is added by registering a
+"head", "block", "conv") and kind -> class.  A new kind of part is added by registering a
 class; the framework's files need no change for it."""
 from __future__ import annotations
 
 from .spec import PartSpec
 
-ROLES = ("mixer", "ffn", "norm", "position", "embedding", "head", "block")
+ROLES = ("mixer", "ffn", "norm", "position", "embedding", "head", "block", "conv")
 _PARTS: dict[tuple[str, str], type] = {}
 
 

@@ -27,10 +27,13 @@ class LayerSpec:
                  `norm1`, `mixer`, `norm2`, `ffn`; an arrangement with a third norm or with two branches
                  side by side names more places and needs no change here.
     arrangement  the block class (registered under the role "block") that reads `parts`.
+    params       constants of the arrangement itself (a multiplier on the branches as they join the stream),
+                 handed to the block class as keyword arguments.
     """
     prefix: str
     parts: Mapping[str, PartSpec]
     arrangement: str = "pre_norm"
+    params: Mapping[str, Any] = field(default_factory=dict)
 
     def part(self, place: str) -> PartSpec:
         try:
