@@ -70,7 +70,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
                    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, int page_size, float scale, int window,
                    int n_splits, int part_stride, const int* __restrict__ work, const char* next_w, unsigned next_piece,
-                   int early_loads, const float* __restrict__ sink) {
+                   int early_loads, const float* __restrict__ sink, float softcap, int keep_first) {
     constexpr int LD = HD + PAD;                   // shared-memory row length in elements
     constexpr int KD = HD / 16;                    // k16 steps over the head dimension
     constexpr int STAGE = 2 * TILE * LD;           // elements of one tile: K rows, then V rows
@@ -124,22 +124,29 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     const int* pt = page_table + (size_t)slots[tok_seq[tok]] * pt_stride;
 
     const int first_tile = start / TILE;
-    const int n_tiles = (len + TILE - 1) / TILE - first_tile;
-    int tile_lo, tile_hi;
+    // With kept first positions the tiles that a token sees are those of its first `keep_first` keys that lie
+    // ahead of its window (`kept` of them) and then the window's: tiles are counted through both, and a count v
+    // stands for tile v when v < kept and for tile first_tile + v - kept otherwise.  Every counted tile holds a
+    // visible key.
+    const int kept = (window > 0 && keep_first > 0) ? min((keep_first + TILE - 1) / TILE, first_tile) : 0;
+    const int shift = first_tile - kept;
+    const int n_tiles = (len + TILE - 1) / TILE - shift;
+    int tile_lo, tile_hi;           // counts, not tiles
     if (work) {
-        tile_lo = first_tile + seg_lo;
-        tile_hi = min(first_tile + n_tiles, first_tile + seg_hi);
+        tile_lo = seg_lo;
+        tile_hi = min(n_tiles, seg_hi);
     } else {
         const int per_split = (n_tiles + parts - 1) / parts;
-        tile_lo = first_tile + split * per_split;
-        tile_hi = min(first_tile + n_tiles, tile_lo + per_split);
+        tile_lo = split * per_split;
+        tile_hi = min(n_tiles, tile_lo + per_split);
     }
+    auto tile_of = [&](int v) { return v < kept ? v : v + shift; };
 
-    // This warp's tiles are tile_lo + warp, + DW, ...; `n` counts them.
+    // This warp's tiles are those of the counts tile_lo + warp, + DW, ...; `n` counts them.
     auto issue = [&](int n) {
-        const int tile = tile_lo + warp + n * DW;
-        if (tile < tile_hi) {
-            const int kb = tile * TILE;
+        const int v = tile_lo + warp + n * DW;
+        if (v < tile_hi) {
+            const int kb = tile_of(v) * TILE;
             const int page = pt[kb / page_size];
             const size_t off = (size_t)page * Hkv * page_size * hd + head_off + (size_t)(kb % page_size) * hd;
             __nv_bfloat16* ks = my_ring + (size_t)(n % RING) * STAGE;
@@ -160,7 +167,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     bool early = waited || early_loads != 0;       // after the wait nothing of the step is still being written
     if (!waited) {
 #pragma unroll
-        for (int n = 0; n < RING - 1; ++n) early = early && (tile_lo + warp + n * DW != own_tile);
+        for (int n = 0; n < RING - 1; ++n) early = early && (tile_of(tile_lo + warp + n * DW) != own_tile);
     }
     if (early) {
 #pragma unroll
@@ -200,7 +207,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         issue(n + RING - 1);
         cp_async_wait<RING - 1>();
         __syncwarp();
-        const int kb = (tile_lo + warp + n * DW) * TILE;
+        const int kb = tile_of(tile_lo + warp + n * DW) * TILE;
         const __nv_bfloat16* ks = my_ring + (size_t)(n % RING) * STAGE;
         const __nv_bfloat16* vs = ks + TILE * LD;
         // S = Q K^T for the tile's two groups of 8 keys.
@@ -224,9 +231,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 int key = kb + nt * 8 + 2 * t + i;
-                bool ok = key >= start && key < len;
-                s[nt][i] = ok ? s[nt][i] * scale : -CUDART_INF_F;
-                s[nt][2 + i] = ok ? s[nt][2 + i] * scale : -CUDART_INF_F;
+                bool ok = (key >= start || key < keep_first) && key < len;
+                float a = s[nt][i] * scale, b = s[nt][2 + i] * scale;
+                if (softcap > 0.f) {              // score <- c tanh(score / c)
+                    a = softcap * tanhf(a / softcap);
+                    b = softcap * tanhf(b / softcap);
+                }
+                s[nt][i] = ok ? a : -CUDART_INF_F;
+                s[nt][2 + i] = ok ? b : -CUDART_INF_F;
                 tm0 = fmaxf(tm0, s[nt][i]);
                 tm1 = fmaxf(tm1, s[nt][2 + i]);
             }
@@ -235,8 +247,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
         tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 1));
         tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, 2));
         const float nm0 = fmaxf(m0, tm0), nm1 = fmaxf(m1, tm1);
-        // A tile of this warp always holds at least one visible key (kb <= pos, kb + 15 >= start),
-        // so nm0 and nm1 are finite.
+        // A tile of this warp always holds at least one visible key (kb <= pos, and kb + 15 >= start or
+        // kb < keep_first), so nm0 and nm1 are finite.
         const float c0 = expf(m0 - nm0), c1 = expf(m1 - nm1);
         m0 = nm0;
         m1 = nm1;
@@ -396,7 +408,7 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
            const int* tok_pos, const int* tok_seq, const int* slots, float* part_o, float* part_ml, int* counters,
            void* out, int T, int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
            const int* work, int teams, const void* next_w, long next_bytes, int early_loads, const float* sink,
-           cudaStream_t stream) {
+           float softcap, int keep_first, cudaStream_t stream) {
     int G = H / Hkv, gtiles = (G + 15) / 16;
     dim3 grid(n_splits, Hkv * gtiles, T);
     if (work) grid = dim3(Hkv * gtiles, teams, 1);      // n_splits is then the room for parts per token in the scratch
@@ -416,7 +428,7 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
     int rc = launch_pdl(attn_decode_kernel<HD>, grid, dim3(DW * 32), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
         part_o, part_ml, counters, (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, n_splits, n_splits, work,
-        (const char*)next_w, (unsigned)piece, early_loads, sink);
+        (const char*)next_w, (unsigned)piece, early_loads, sink, softcap, keep_first);
     if (rc != LQ_OK || n_splits == 1 || counters != nullptr) return rc;
     return launch_pdl(attn_merge_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
                       (__nv_bfloat16*)out, hd, n_splits, H, sink);
@@ -450,23 +462,39 @@ bool sizes_ok(int H, int Hkv, int hd, int page_size, int q_stride, int n_splits)
 // parts than that, and the counters are required when any token has more than one part.
 //
 // sink (or null): float32 [H]; each head's softmax denominator gets one more term exp(sink[h]).
+//
+// softcap c (0: none): score <- c tanh(score / c) after the scale.  keep_first n (0: none; with a window): a
+// token's first n keys stay visible when its window has moved past them; the tiles of a token are then counted
+// through the kept tiles ahead of the window and then the window's (a work list's tile ranges are such counts).
+LQ_EXPORT int lq_attn_decode_capped(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                    const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
+                                    const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
+                                    int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
+                                    const int* work, int teams, const void* next_w, long next_bytes, int early_loads,
+                                    const float* sink, float softcap, int keep_first, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (!sizes_ok(H, Hkv, hd, page_size, q_stride, n_splits)) return LQ_BAD_SIZE;
+    if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
+    if (work && (teams < 1 || teams > 65535 || (n_splits > 1 && !counters))) return LQ_BAD_SIZE;
+    if (softcap < 0.f || keep_first < 0) return LQ_BAD_SIZE;
+#define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
+                                    part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
+                                    work, teams, next_w, next_bytes, early_loads, sink, softcap, keep_first, stream)
+    if (hd <= 32) LQ_GO(32);
+    if (hd <= 64) LQ_GO(64);
+    LQ_GO(128);
+#undef LQ_GO
+}
+
 LQ_EXPORT int lq_attn_decode_sink(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                   const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                   const int* slots, float* part_o, float* part_ml, int* counters, void* out, int T,
                                   int H, int Hkv, int hd, int page_size, float scale, int window, int n_splits,
                                   const int* work, int teams, const void* next_w, long next_bytes, int early_loads,
                                   const float* sink, cudaStream_t stream) {
-    if (T <= 0) return LQ_OK;
-    if (!sizes_ok(H, Hkv, hd, page_size, q_stride, n_splits)) return LQ_BAD_SIZE;
-    if (n_splits > 1 && (!part_o || !part_ml)) return LQ_BAD_SIZE;
-    if (work && (teams < 1 || teams > 65535 || (n_splits > 1 && !counters))) return LQ_BAD_SIZE;
-#define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, \
-                                    part_o, part_ml, counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, \
-                                    work, teams, next_w, next_bytes, early_loads, sink, stream)
-    if (hd <= 32) LQ_GO(32);
-    if (hd <= 64) LQ_GO(64);
-    LQ_GO(128);
-#undef LQ_GO
+    return lq_attn_decode_capped(q, q_stride, k_pages, v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, part_o, part_ml,
+                                 counters, out, T, H, Hkv, hd, page_size, scale, window, n_splits, work, teams, next_w,
+                                 next_bytes, early_loads, sink, 0.f, 0, stream);
 }
 
 LQ_EXPORT int lq_attn_decode_work(const void* q, int q_stride, const void* k_pages, const void* v_pages,

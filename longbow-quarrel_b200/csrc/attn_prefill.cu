@@ -43,6 +43,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// tanh(x) = 1 - 2 / (e^(2x) + 1) by two operations of the special-function unit: absolute error about 3e-7.
+__device__ __forceinline__ float tanh_fast(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.885390081777927f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(-2.0f, r, 1.0f);
+}
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -56,7 +63,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
                     const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ page_table, int pt_stride,
                     const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
                     const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
-                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, float scale_log2, int window, const float* __restrict__ sink) {
+                    __nv_bfloat16* __restrict__ out, int H, int Hkv, int hd, float scale_log2, int window, const float* __restrict__ sink,
+                    float cap_pre, int keep_first) {
     constexpr int LD = HD + PAD;                       // shared-memory row length in elements
     constexpr int KD = HD / 16;                        // k16 steps over the head dimension
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -76,7 +84,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
     const int* pt = page_table + (size_t)slots[seq] * pt_stride;
     const int pos_last = pos0 + n_rows - 1;
     const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
-    const int tile_lo = key_first / BLOCK_N, tile_hi = pos_last / BLOCK_N;       // inclusive
+    // With kept first positions the block walks the tiles of the first `keep_first` keys that lie ahead of its
+    // window (`kept` of them) and then the window's: step n stands for tile n when n < kept, else tile_lo - kept + n.
+    const int tile_lo = key_first / BLOCK_N;
+    const int kept = (window > 0 && keep_first > 0) ? min((keep_first + BLOCK_N - 1) / BLOCK_N, tile_lo) : 0;
+    const int n_tiles = pos_last / BLOCK_N - tile_lo + 1 + kept;
+    auto tile_at = [&](int n) { return n < kept ? n : tile_lo - kept + n; };
 
     // ---- loads
     auto load_q = [&]() {
@@ -100,7 +113,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
         }
     };
     load_q();
-    load_kv(tile_lo, 0);
+    load_kv(tile_at(0), 0);
     cp_async_commit();
 
     float o[HD / 8][4];
@@ -116,13 +129,13 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
     const int warp_pos_hi = min(pos_last, pos0 + warp * 16 + 15);        // last position any row of the warp has
     const int warp_key_lo = (window > 0) ? max(0, pos0 + warp * 16 - window + 1) : 0;
 
-    for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-        const int stage = (tile - tile_lo) & 1;
-        if (tile + 1 <= tile_hi) load_kv(tile + 1, stage ^ 1);
+    for (int n = 0; n < n_tiles; ++n) {
+        const int stage = n & 1, tile = tile_at(n);
+        if (n + 1 < n_tiles) load_kv(tile_at(n + 1), stage ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        if (tile == tile_lo) {
+        if (n == 0) {
 #pragma unroll
             for (int kk = 0; kk < KD; ++kk) {
                 // A fragment of Q: matrices (rows 0-7, d 0-7), (rows 8-15, d 0-7), (rows 0-7, d 8-15), (rows 8-15, d 8-15)
@@ -131,7 +144,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
             }
         }
         const int kb = tile * BLOCK_N;
-        if (kb <= warp_pos_hi && kb + BLOCK_N > warp_key_lo) {
+        // A warp skips the tiles that lie wholly ahead of its rows' windows, unless they hold kept first keys
+        // (the block's first window tile may still hold some for a warp whose own window starts later).
+        if (kb <= warp_pos_hi && (kb + BLOCK_N > warp_key_lo || kb < keep_first)) {
             const __nv_bfloat16* ks = sk + stage * BLOCK_N * LD;
             const __nv_bfloat16* vs = sv + stage * BLOCK_N * LD;
             float s[8][4];
@@ -159,10 +174,15 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     int key = kb + j * 8 + 2 * t + i;
-                    bool ok0 = row0ok && key <= prow0 && (window <= 0 || key > prow0 - window);
-                    bool ok1 = row1ok && key <= prow1 && (window <= 0 || key > prow1 - window);
-                    s[j][i] = ok0 ? s[j][i] * scale_log2 : -CUDART_INF_F;
-                    s[j][2 + i] = ok1 ? s[j][2 + i] * scale_log2 : -CUDART_INF_F;
+                    bool ok0 = row0ok && key <= prow0 && (window <= 0 || key > prow0 - window || key < keep_first);
+                    bool ok1 = row1ok && key <= prow1 && (window <= 0 || key > prow1 - window || key < keep_first);
+                    float a = s[j][i], b = s[j][2 + i];
+                    if (cap_pre > 0.f) {          // capped scores: tanh(s scale / c); scale_log2 is then c log2(e)
+                        a = tanh_fast(a * cap_pre);
+                        b = tanh_fast(b * cap_pre);
+                    }
+                    s[j][i] = ok0 ? a * scale_log2 : -CUDART_INF_F;
+                    s[j][2 + i] = ok1 ? b * scale_log2 : -CUDART_INF_F;
                     tm0 = fmaxf(tm0, s[j][i]);
                     tm1 = fmaxf(tm1, s[j][2 + i]);
                 }
@@ -238,7 +258,7 @@ template <int HD>
 int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages, const int* page_table, int pt_stride,
            const int* slots, const int* kv_len, const int* qb_seq, const int* qb_row, const int* qb_rows,
            const int* qb_pos, void* out, int n_blocks, int H, int Hkv, int hd, float scale, int window,
-           const float* sink, cudaStream_t stream) {
+           const float* sink, float softcap, int keep_first, cudaStream_t stream) {
     constexpr size_t smem = (size_t)(BLOCK_M + 4 * BLOCK_N) * (HD + PAD) * 2;
     static bool configured = false;
     if (!configured) {
@@ -249,7 +269,8 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
     dim3 grid(n_blocks * H);
     return launch_pdl(attn_prefill_kernel<HD>, grid, dim3(NT), smem, stream, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
-        qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv, hd, scale * 1.4426950408889634f, window, sink);
+        qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv, hd, (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, window, sink,
+        softcap > 0.f ? scale / softcap : 0.f, keep_first);
 }
 
 }  // namespace
@@ -258,17 +279,29 @@ int launch(const void* q, int q_stride, const void* k_pages, const void* v_pages
 // qb_*: the work list, n_blocks entries: sequence, first packed row, rows (<= 64), position of the first row.
 // head_dim a multiple of 8 and at most 128; the cache's page size must be 64.
 // sink (or null): float32 [H]; each head's softmax denominator gets one more term exp(sink[h]).
+// softcap c (0: none): score <- c tanh(score / c) after the scale.  keep_first n (0: none; with a window): a row's
+// first n keys stay visible when its window has moved past them.
+LQ_EXPORT int lq_attn_prefill_capped(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                     const int* page_table, int pt_stride, const int* slots, const int* kv_len,
+                                     const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos, void* out,
+                                     int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
+                                     const float* sink, float softcap, int keep_first, cudaStream_t stream) {
+    if (n_blocks <= 0) return LQ_OK;
+    if (softcap < 0.f || keep_first < 0) return LQ_BAD_SIZE;
+    if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size != BLOCK_N || q_stride % 8) return LQ_BAD_SIZE;
+#define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row, \
+                                    qb_rows, qb_pos, out, n_blocks, H, Hkv, hd, scale, window, sink, softcap, keep_first, stream)
+    if (hd <= 32) LQ_GO(32);
+    if (hd <= 64) LQ_GO(64);
+    LQ_GO(128);
+#undef LQ_GO
+}
+
 LQ_EXPORT int lq_attn_prefill(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                               const int* page_table, int pt_stride, const int* slots, const int* kv_len,
                               const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos, void* out,
                               int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
                               const float* sink, cudaStream_t stream) {
-    if (n_blocks <= 0) return LQ_OK;
-    if (hd % 8 || hd > 128 || hd <= 0 || H % Hkv || page_size != BLOCK_N || q_stride % 8) return LQ_BAD_SIZE;
-#define LQ_GO(HD) return launch<HD>(q, q_stride, k_pages, v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row, \
-                                    qb_rows, qb_pos, out, n_blocks, H, Hkv, hd, scale, window, sink, stream)
-    if (hd <= 32) LQ_GO(32);
-    if (hd <= 64) LQ_GO(64);
-    LQ_GO(128);
-#undef LQ_GO
+    return lq_attn_prefill_capped(q, q_stride, k_pages, v_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows,
+                                  qb_pos, out, n_blocks, H, Hkv, hd, page_size, scale, window, sink, 0.f, 0, stream);
 }

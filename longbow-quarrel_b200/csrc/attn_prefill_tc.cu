@@ -82,6 +82,13 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// tanh(x) = 1 - 2 / (e^(2x) + 1) by two operations of the special-function unit: absolute error about 3e-7.
+__device__ __forceinline__ float tanh_fast(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(ex2(x * 2.885390081777927f) + 1.0f));
+    return fmaf(-2.0f, r, 1.0f);
+}
+
 #define LQ_WAIT(bar, parity, code) \
     if (!mbar_wait(smem_u32(&(bar)), (parity))) { give_up(code); ok = false; }
 
@@ -92,7 +99,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
                        const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
                        __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window,
-                        const float* __restrict__ sink) {
+                       const float* __restrict__ sink, float cap_pre, int keep_first) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int DH = HD / 64;                  // panels of 64 elements along the head dimension
     Smem<HD>& sm = *reinterpret_cast<Smem<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -131,7 +138,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int* pt = page_table + (size_t)slots[seq] * pt_stride;
     const int pos_last = pos0 + n_rows - 1;
     const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
-    const int tile_lo = key_first / BN, n_tiles = pos_last / BN - tile_lo + 1;
+    // With kept first positions the block walks the tiles of the first `keep_first` keys that lie ahead of its
+    // window (`kept` of them) and then the window's: step j stands for tile j when j < kept, else tile_lo - kept + j.
+    const int tile_lo = key_first / BN;
+    const int kept = (window > 0 && keep_first > 0) ? min((keep_first + BN - 1) / BN, tile_lo) : 0;
+    const int n_tiles = pos_last / BN - tile_lo + 1 + kept;
+    auto tile_at = [&](int j) { return j < kept ? j : tile_lo - kept + j; };
     const int last_page = (len - 1) / PAGE;
 
     if (warp == 0) {
@@ -147,7 +159,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!ok) break;
                 int rows[2];
                 for (int i = 0; i < 2; ++i) {
-                    const int pg = (tile_lo + j) * 2 + i;
+                    const int pg = tile_at(j) * 2 + i;
                     const int page = pg <= last_page ? pt[pg] : -1;
                     rows[i] = page >= 0 ? (page * Hkv + kvh) * PAGE : oob_row;   // out of range: TMA fills zeros
                 }
@@ -228,10 +240,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             wait_ld();
             fence_before();
             mbar_arrive(smem_u32(&sm.s_empty));          // S may be overwritten by the next tile's product
-            const int kb = (tile_lo + j) * BN + part * NC;
+            const int tb = tile_at(j) * BN, kb = tb + part * NC;
+            if (cap_pre > 0.f) {                          // capped scores: t <- tanh(t scale / c); scale_log2 is then c log2(e)
+#pragma unroll
+                for (int c = 0; c < NC; ++c) t[c] = tanh_fast(t[c] * cap_pre);
+            }
             // Tiles that lie wholly inside every row's range (most of them) need no mask.
-            const bool whole = n_rows == BM && (tile_lo + j) * BN + BN - 1 <= pos0 && (tile_lo + j) * BN + BN <= len &&
-                               (window <= 0 || (tile_lo + j) * BN > pos_last - window);
+            const bool whole = n_rows == BM && tb + BN - 1 <= pos0 && tb + BN <= len && (window <= 0 || tb > pos_last - window);
             // Maxima of the raw scores (the scale is positive: it is applied to the maximum, and to the scores
             // inside the exponent's multiply-add).
             float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
@@ -242,7 +257,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     const int key = kb + c;
-                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window);
+                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window || key < keep_first);
                     t[c] = vis ? t[c] : -CUDART_INF_F;
                     mx[c & 3] = fmaxf(mx[c & 3], t[c]);
                 }
@@ -368,7 +383,7 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int* __restrict__ slots, const int* __restrict__ kv_len, const int* __restrict__ qb_seq,
                         const int* __restrict__ qb_row, const int* __restrict__ qb_rows, const int* __restrict__ qb_pos,
                         __nv_bfloat16* __restrict__ out, int H, int Hkv, int oob_row, float scale_log2, int window,
-                        const float* __restrict__ sink) {
+                        const float* __restrict__ sink, float cap_pre, int keep_first) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int DH = HD / 64;
     Smem2<HD>& sm = *reinterpret_cast<Smem2<HD>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -406,7 +421,12 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int* pt = page_table + (size_t)slots[seq] * pt_stride;
     const int pos_last = pos0 + n_rows - 1;
     const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
-    const int tile_lo = key_first / BN, n_tiles = pos_last / BN - tile_lo + 1;
+    // With kept first positions the block walks the tiles of the first `keep_first` keys that lie ahead of its
+    // window (`kept` of them) and then the window's: step j stands for tile j when j < kept, else tile_lo - kept + j.
+    const int tile_lo = key_first / BN;
+    const int kept = (window > 0 && keep_first > 0) ? min((keep_first + BN - 1) / BN, tile_lo) : 0;
+    const int n_tiles = pos_last / BN - tile_lo + 1 + kept;
+    auto tile_at = [&](int j) { return j < kept ? j : tile_lo - kept + j; };
     const int last_page = (len - 1) / PAGE;
 
     if (warp < 4) {
@@ -424,7 +444,7 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!ok) break;
                 int rows[2];
                 for (int i = 0; i < 2; ++i) {
-                    const int pg = (tile_lo + j) * 2 + i;
+                    const int pg = tile_at(j) * 2 + i;
                     const int page = pg <= last_page ? pt[pg] : -1;
                     rows[i] = page >= 0 ? (page * Hkv + kvh) * PAGE : oob_row;   // out of range: TMA fills zeros
                 }
@@ -500,7 +520,11 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) ld32(tmem_s + c * 32, reinterpret_cast<uint32_t*>(t) + c * 32);
             wait_ld();
-            const int kb = (tile_lo + j) * BN;
+            const int kb = tile_at(j) * BN;
+            if (cap_pre > 0.f) {                          // capped scores: t <- tanh(t scale / c); scale_log2 is then c log2(e)
+#pragma unroll
+                for (int c = 0; c < BN; ++c) t[c] = tanh_fast(t[c] * cap_pre);
+            }
             const bool whole = n_rows == BM && kb + BN - 1 <= pos0 && kb + BN <= len && (window <= 0 || kb > pos_last - window);
             float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (whole) {
@@ -510,7 +534,7 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int key = kb + c;
-                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window);
+                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window || key < keep_first);
                     t[c] = vis ? t[c] : -CUDART_INF_F;
                     mx[c & 3] = fmaxf(mx[c & 3], t[c]);
                 }
@@ -590,8 +614,11 @@ template <int HD>
 int launch_hd(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages, int n_pages,
               const int* page_table, int pt_stride, const int* slots, const int* kv_len, const int* qb_seq,
               const int* qb_row, const int* qb_rows, const int* qb_pos, void* out, int n_blocks, int H, int Hkv,
-              float scale, int window, const float* sink, cudaStream_t stream) {
+              float scale, int window, const float* sink, float softcap, int keep_first, cudaStream_t stream) {
     CUtensorMap mq, mk, mv;
+    // Capped scores: the kernels take tanh(s scale / c) and multiply by c log2(e) inside the exponent.
+    const float cap_pre = softcap > 0.f ? scale / softcap : 0.f;
+    const float scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
     const long kv_rows = (long)n_pages * Hkv * PAGE;
     int rc = make_map_bf16(&mq, q, T, q_stride, q_stride, BM);
     if (rc == LQ_OK) rc = make_map_bf16(&mk, k_pages, kv_rows, HD, HD, PAGE);
@@ -617,11 +644,11 @@ int launch_hd(const void* q, int q_stride, int T, const void* k_pages, const voi
         }
         return launch_pdl(attn_prefill_two_kernel<HD>, dim3(n_blocks * (H / 2)), dim3(N_THREADS2), smem2, stream, mq, mk, mv,
                           page_table, pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
-                          (int)kv_rows, scale * 1.4426950408889634f, window, sink);
+                          (int)kv_rows, scale_log2, window, sink, cap_pre, keep_first);
     }
     return launch_pdl(attn_prefill_tc_kernel<HD>, dim3(n_blocks * H), dim3(N_THREADS), smem, stream, mq, mk, mv, page_table,
                       pt_stride, slots, kv_len, qb_seq, qb_row, qb_rows, qb_pos, (__nv_bfloat16*)out, H, Hkv,
-                      (int)kv_rows, scale * 1.4426950408889634f, window, sink);
+                      (int)kv_rows, scale_log2, window, sink, cap_pre, keep_first);
 }
 }  // namespace
 
@@ -629,18 +656,31 @@ int launch_hd(const void* q, int q_stride, int T, const void* k_pages, const voi
 // k_pages, v_pages: [n_pages, Hkv, 64, hd] bfloat16 of one cache entry, finite everywhere.
 // qb_*: the work list, n_blocks entries: sequence, first packed row, rows (<= 128), position of the first row.
 // sink (or null): float32 [H]; each head's softmax denominator gets one more term exp(sink[h]).
+// softcap c (0: none): score <- c tanh(score / c) after the scale.  keep_first n (0: none; with a window): a row's
+// first n keys stay visible when its window has moved past them.
+LQ_EXPORT int lq_attn_prefill_tc_capped(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages,
+                                 int n_pages, const int* page_table, int pt_stride, const int* slots, const int* kv_len,
+                                 const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos, void* out,
+                                 int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
+                                 const float* sink, float softcap, int keep_first, cudaStream_t stream) {
+    if (n_blocks <= 0) return LQ_OK;
+    if (softcap < 0.f || keep_first < 0 || scale <= 0.f) return LQ_BAD_SIZE;
+    if ((hd != 64 && hd != 128) || page_size != PAGE || H % Hkv || q_stride % 8 || ((uintptr_t)q & 15)) return LQ_BAD_SIZE;
+    if (hd == 64)
+        return launch_hd<64>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
+                             qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, sink, softcap, keep_first, stream);
+    return launch_hd<128>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
+                          qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, sink, softcap, keep_first, stream);
+}
+
 LQ_EXPORT int lq_attn_prefill_tc(const void* q, int q_stride, int T, const void* k_pages, const void* v_pages,
                                  int n_pages, const int* page_table, int pt_stride, const int* slots, const int* kv_len,
                                  const int* qb_seq, const int* qb_row, const int* qb_rows, const int* qb_pos, void* out,
                                  int n_blocks, int H, int Hkv, int hd, int page_size, float scale, int window,
                                  const float* sink, cudaStream_t stream) {
-    if (n_blocks <= 0) return LQ_OK;
-    if ((hd != 64 && hd != 128) || page_size != PAGE || H % Hkv || q_stride % 8 || ((uintptr_t)q & 15)) return LQ_BAD_SIZE;
-    if (hd == 64)
-        return launch_hd<64>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
-                             qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, sink, stream);
-    return launch_hd<128>(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq, qb_row,
-                          qb_rows, qb_pos, out, n_blocks, H, Hkv, scale, window, sink, stream);
+    return lq_attn_prefill_tc_capped(q, q_stride, T, k_pages, v_pages, n_pages, page_table, pt_stride, slots, kv_len, qb_seq,
+                                     qb_row, qb_rows, qb_pos, out, n_blocks, H, Hkv, hd, page_size, scale, window, sink, 0.f, 0,
+                                     stream);
 }
 
 LQ_EXPORT int lq_attn_prefill_tc_status() { return tc::status_read(); }

@@ -207,6 +207,7 @@ __global__ void __launch_bounds__(1024) group_rows_kernel(const int* __restrict_
 // The same list with every group's rows padded to whole tiles of `tile` rows, for a product whose row tiles each
 // belong to one group: src [cap] = the index that stands at each padded place (-1: padding), dst [n] = the place of
 // each index, tile_group [cap / tile] = each tile's group (-1 behind the last).  cap = (ceil(n / tile) + G) * tile holds every case.
+// Indices whose group is G or above (groups without rows of their own) take no place: their dst is -1.
 __global__ void __launch_bounds__(1024) group_rows_padded_kernel(const int* __restrict__ ids, int n, int G, int tile, int cap,
                                                                  int* __restrict__ src, int* __restrict__ dst,
                                                                  int* __restrict__ tile_group) {
@@ -218,7 +219,8 @@ __global__ void __launch_bounds__(1024) group_rows_padded_kernel(const int* __re
     for (int g = threadIdx.x; g < G; g += blockDim.x) count[g] = 0;
     for (int i = threadIdx.x; i < cap; i += blockDim.x) src[i] = -1;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        if (ids[i] < G) atomicAdd(&count[ids[i]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -232,6 +234,10 @@ __global__ void __launch_bounds__(1024) group_rows_padded_kernel(const int* __re
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        if (ids[i] >= G) {
+            dst[i] = -1;
+            continue;
+        }
         const int p = atomicAdd(&cursor[ids[i]], 1);
         src[p] = i;
         dst[i] = p;
@@ -248,35 +254,27 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
         out[(size_t)p * row16 + i] = s >= 0 ? a[(size_t)(s / div) * row16 + i] : make_uint4(0, 0, 0, 0);
 }
 
-// x[t, :] (+)= sum_j weights[t, j] y[place(t * top + j), :] ... with `place` = dst of the padded order (null: the pair itself)
-__global__ void __launch_bounds__(256) moe_combine_at_kernel(const float* __restrict__ y, const int* __restrict__ place,
-                                                             const float* __restrict__ weights, const float* __restrict__ shared,
-                                                             const float* __restrict__ zs, int zs_stride, float* __restrict__ x,
-                                                             int accumulate, int top, int D) {
+// x[t, :] (+)= sum_j weights[t, j] y[row(t, j), :] (+ shared_scale * sigmoid(zs[t]) * shared[t, :]), the choices added in
+// their order.  row(t, j) = place[t * top + j] with `place` (the dst of the padded order), else the pair t * top + j itself.
+// With `ids` and `h`, a pair whose id is E or above has no row in y: it adds weights[t, j] * h[t, :] (an expert that passes
+// its input on).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place,
+                                                          const float* __restrict__ weights, const float* __restrict__ shared,
+                                                          const float* __restrict__ zs, int zs_stride, float* __restrict__ x,
+                                                          int accumulate, int top, int D, const int* __restrict__ ids, int E,
+                                                          const __nv_bfloat16* __restrict__ h, float shared_scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const float sg = (shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f;
+    const float sg = shared_scale * ((shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f);
     for (int d = threadIdx.x; d < D; d += 256) {
         float s = 0.f;
-        for (int j = 0; j < top; ++j) s = fmaf(weights[(size_t)t * top + j], y[(size_t)place[t * top + j] * D + d], s);
-        if (shared) s = fmaf(sg, shared[(size_t)t * D + d], s);
-        float* o = x + (size_t)t * D + d;
-        *o = accumulate ? *o + s : s;
-    }
-}
-
-// x[t, :] (+)= sum_j weights[t, j] y[t * top + j, :] (+ sigmoid(zs[t]) * shared[t, :]), the choices added in their order.
-__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights,
-                                                          const float* __restrict__ shared, const float* __restrict__ zs,
-                                                          int zs_stride, float* __restrict__ x, int accumulate, int top, int D) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int t = blockIdx.x;
-    const float sg = (shared && zs) ? 1.f / (1.f + expf(-zs[(size_t)t * zs_stride])) : 1.f;
-    for (int d = threadIdx.x; d < D; d += 256) {
-        float s = 0.f;
-        for (int j = 0; j < top; ++j) s = fmaf(weights[(size_t)t * top + j], y[((size_t)t * top + j) * D + d], s);
+        for (int j = 0; j < top; ++j) {
+            const size_t pair = (size_t)t * top + j;
+            const float v = (ids && ids[pair] >= E) ? __bfloat162float(h[(size_t)t * D + d])
+                                                    : y[(place ? (size_t)place[pair] : pair) * D + d];
+            s = fmaf(weights[pair], v, s);
+        }
         if (shared) s = fmaf(sg, shared[(size_t)t * D + d], s);
         float* o = x + (size_t)t * D + d;
         *o = accumulate ? *o + s : s;
@@ -330,14 +328,22 @@ LQ_EXPORT int lq_gather_rows(const void* a, const int* src, int div, void* out, 
     return launch_pdl(gather_rows_kernel, dim3(cap), dim3(256), 0, stream, (const uint4*)a, src, div, (uint4*)out, cap, row_bytes / 16);
 }
 
+// ids (with E and h, bfloat16 [T, D]) or null; place or null: see moe_combine_kernel.
+LQ_EXPORT int lq_moe_combine_more(const float* y, const int* place, const float* weights, const float* shared, const float* zs,
+                                  int zs_stride, float* x, int accumulate, int T, int top, int D, const int* ids, int E,
+                                  const void* h, float shared_scale, cudaStream_t stream) {
+    if (T <= 0) return LQ_OK;
+    if (ids && !h) return LQ_BAD_SIZE;
+    return launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, place, weights, shared, zs, zs_stride, x, accumulate,
+                      top, D, ids, E, (const __nv_bfloat16*)h, shared_scale);
+}
+
 LQ_EXPORT int lq_moe_combine_at(const float* y, const int* place, const float* weights, const float* shared, const float* zs,
                                 int zs_stride, float* x, int accumulate, int T, int top, int D, cudaStream_t stream) {
-    if (T <= 0) return LQ_OK;
-    return launch_pdl(moe_combine_at_kernel, dim3(T), dim3(256), 0, stream, y, place, weights, shared, zs, zs_stride, x, accumulate, top, D);
+    return lq_moe_combine_more(y, place, weights, shared, zs, zs_stride, x, accumulate, T, top, D, nullptr, 0, nullptr, 1.f, stream);
 }
 
 LQ_EXPORT int lq_moe_combine(const float* y, const float* weights, const float* shared, const float* zs, int zs_stride, float* x,
                              int accumulate, int T, int top, int D, cudaStream_t stream) {
-    if (T <= 0) return LQ_OK;
-    return launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, stream, y, weights, shared, zs, zs_stride, x, accumulate, top, D);
+    return lq_moe_combine_more(y, nullptr, weights, shared, zs, zs_stride, x, accumulate, T, top, D, nullptr, 0, nullptr, 1.f, stream);
 }

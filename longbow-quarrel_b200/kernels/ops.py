@@ -1083,10 +1083,11 @@ def _check_sink(sink, H: int):
 
 def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, query_blocks, H: int, Hkv: int, hd: int,
                  page_size: int, scale: float, window: int | None, out: torch.Tensor | None = None,
-                 sink: torch.Tensor | None = None) -> torch.Tensor:
+                 sink: torch.Tensor | None = None, softcap: float | None = None, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of blocks of query rows over the paged bfloat16 cache (flash style:
     tensor-core products, online softmax in float32).  query_blocks = (sequence, first row,
-    rows, first position) int32 tensors, one entry for each block of at most 64 rows."""
+    rows, first position) int32 tensors, one entry for each block of at most 64 rows.  softcap c: score <-
+    c tanh(score / c) after the scale; keep_first n (with a window): a row's first n keys stay visible."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_prefill takes bfloat16 queries and cache")
@@ -1095,21 +1096,24 @@ def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, q
     if out is None:
         out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
     qb_seq, qb_row, qb_rows, qb_pos = query_blocks
-    fn = _fn("attn_prefill", "lq_attn_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                 c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    fn = _fn("attn_prefill", "lq_attn_prefill_capped", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                        c_int, c_int, c_float, c_int, c_void_p, c_float, c_int, c_void_p])
     _check_sink(sink, H)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(slots), _p(kv_len),
               _p(qb_seq), _p(qb_row), _p(qb_rows), _p(qb_pos), _p(out), qb_seq.numel(), H, Hkv, hd, page_size,
-              float(scale), int(window or 0), _p(sink), _stream()), "attn_prefill")
+              float(scale), int(window or 0), _p(sink), float(softcap or 0.0), int(keep_first if window else 0), _stream()),
+           "attn_prefill")
     return out
 
 
 def attn_prefill_tc(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, query_blocks128, H: int, Hkv: int,
                     hd: int, page_size: int, scale: float, window: int | None,
-                    out: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor | None = None, sink: torch.Tensor | None = None, softcap: float | None = None,
+                    keep_first: int = 0) -> torch.Tensor:
     """attn_prefill on the tcgen05 tensor cores (TMA-fed, S and O in tensor memory): blocks of at
-    most 128 query rows, head_dim 64 or 128, pages of 64 keys, a cache that is finite everywhere."""
+    most 128 query rows, head_dim 64 or 128, pages of 64 keys, a cache that is finite everywhere.  softcap and
+    keep_first as in attn_prefill."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_tc takes bfloat16 queries and cache")
@@ -1118,13 +1122,14 @@ def attn_prefill_tc(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len
     if out is None:
         out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=q.device)
     qb_seq, qb_row, qb_rows, qb_pos = query_blocks128
-    fn = _fn("attn_prefill_tc", "lq_attn_prefill_tc", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    fn = _fn("attn_prefill_tc", "lq_attn_prefill_tc_capped",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_float, c_int, c_void_p])
     _check_sink(sink, H)
     _check(fn(_p(q), q.stride(0), T, _p(_contig(k_pages, "k_pages")), _p(_contig(v_pages, "v_pages")), k_pages.shape[0],
               _p(page_table), page_table.stride(0), _p(slots), _p(kv_len), _p(qb_seq), _p(qb_row), _p(qb_rows), _p(qb_pos),
-              _p(out), qb_seq.numel(), H, Hkv, hd, page_size, float(scale), int(window or 0), _p(sink), _stream()), "attn_prefill_tc")
+              _p(out), qb_seq.numel(), H, Hkv, hd, page_size, float(scale), int(window or 0), _p(sink), float(softcap or 0.0),
+              int(keep_first if window else 0), _stream()), "attn_prefill_tc")
     return out
 
 
@@ -1138,7 +1143,8 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
                 page_size: int, scale: float, window: int | None, n_splits: int,
                 out: torch.Tensor | None = None, scratch: tuple | None = None,
                 next_w: torch.Tensor | None = None, early_loads: bool = False,
-                work: torch.Tensor | None = None, teams: int = 0, sink: torch.Tensor | None = None) -> torch.Tensor:
+                work: torch.Tensor | None = None, teams: int = 0, sink: torch.Tensor | None = None,
+                softcap: float | None = None, keep_first: int = 0) -> torch.Tensor:
     """Attention of single query rows over the paged bfloat16 cache, the keys of each
     sequence cut into n_splits slices that are merged afterwards.  With `work` (int32: teams + 1 offsets,
     then (token, first tile, last tile + 1, part, parts) per segment) the grid is `teams` blocks per kv
@@ -1147,7 +1153,9 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
     stream reads after this; their first bytes are asked into L2 as the blocks finish.
     early_loads: of the keys and values a row reads, only those at its own position can have been
     written by the kernel ahead on the stream (a decode step: one new token per sequence); the kernel
-    then requests the others without waiting for that kernel."""
+    then requests the others without waiting for that kernel.  softcap c: score <- c tanh(score / c) after the
+    scale.  keep_first n (with a window): a token's first n keys stay visible once its window has moved past them;
+    the tiles that a work list counts are then the kept tiles ahead of the window and after them the window's."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_decode takes bfloat16 queries and cache")
@@ -1175,15 +1183,15 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
                              or work.numel() < teams + 1 + 5 * T):
         raise KernelError("attn_decode: the work list must be int32 with teams + 1 offsets and at least a segment per token")
     _check_sink(sink, H)
-    fn = _fn("attn_decode", "lq_attn_decode_sink", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                                    c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int,
-                                                    c_void_p, c_long, c_int, c_void_p, c_void_p])
+    fn = _fn("attn_decode", "lq_attn_decode_capped", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                      c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int,
+                                                      c_void_p, c_long, c_int, c_void_p, c_float, c_int, c_void_p])
     next_p, next_n = _next(next_w, PREFETCH_BYTES_ATTN)
     _check(fn(_p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0), _p(tok_pos),
               _p(tok_seq), _p(slots), _p(part_o), _p(part_ml), _p(counters), _p(out), T, H, Hkv, hd, page_size,
               float(scale), int(window or 0), n_splits, _p(work), int(teams), next_p, next_n, int(early_loads), _p(sink),
-              _stream()),
+              float(softcap or 0.0), int(keep_first if window else 0), _stream()),
            "attn_decode", 2 if n_splits > 1 and counters is None else 1,
            "attn_decode:teams" if work is not None else "attn_decode:one_slice" if n_splits == 1 else "attn_decode:slices")
     return out

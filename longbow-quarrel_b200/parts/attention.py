@@ -102,7 +102,7 @@ class Attention(Mixer):
 
     def step_needs(self):
         return attention_kernels.step_needs(self.runtime.act_dtype, self.hd, self.H, self.Hkv, self.window,
-                                            self.runtime.device)
+                                            self.runtime.device, keep_first=self.keep_first)
 
     def weights(self):
         n = self.names
