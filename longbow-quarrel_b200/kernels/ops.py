@@ -610,9 +610,10 @@ GROUP_TILE = 128       # rows of a tile of gemm_tc: the padded order gives every
 
 
 def group_rows_padded(ids: torch.Tensor, G: int) -> tuple:
-    """ids int32 [n], each in [0, G) -> (src [cap], dst [n], tile_group [cap / 128]) on the device: the indices group by
-    group with every group padded to whole tiles of 128 places (src: the index at each place, -1 for padding; dst: the
-    place of each index; tile_group: each tile's group, -1 behind the last)."""
+    """ids int32 [n] -> (src [cap], dst [n], tile_group [cap / 128]) on the device: the indices group by group with
+    every group padded to whole tiles of 128 places (src: the index at each place, -1 for padding; dst: the place of
+    each index; tile_group: each tile's group, -1 behind the last).  An index whose id is G or above (a group without
+    rows of its own) takes no place: its dst is -1."""
     n = ids.numel()
     cap = (-(-n // GROUP_TILE) + G) * GROUP_TILE
     src = torch.empty(cap, dtype=torch.int32, device=ids.device)
@@ -651,25 +652,25 @@ def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, accumulate: bool = True,
                 shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None,
-                place: torch.Tensor | None = None) -> torch.Tensor:
-    """x[t] (+)= sum_j weights[t, j] y[t * top + j] (+ sigmoid(shared_gate[t]) * shared[t]); y float32 [T * top, D].
-    place int32 [T * top]: the row of y that holds pair t * top + j (y then has any number of rows)."""
+                place: torch.Tensor | None = None, ids: torch.Tensor | None = None, E: int = 0,
+                h: torch.Tensor | None = None, shared_scale: float = 1.0) -> torch.Tensor:
+    """x[t] (+)= sum_j weights[t, j] y[t * top + j] (+ shared_scale * sigmoid(shared_gate[t]) * shared[t]); y float32
+    [T * top, D].  place int32 [T * top]: the row of y that holds pair t * top + j (y then has any number of rows).
+    ids int32 [T, top] with E and h (bfloat16 [T, D]): a pair whose id is E or above has no row in y and adds
+    weights[t, j] * h[t] instead (an expert that passes its input on)."""
     T, top = weights.shape
     D = y.shape[1]
     if y.dtype != torch.float32 or not y.is_contiguous() or tuple(x.shape) != (T, D) or (place is None and y.shape[0] != T * top):
         raise KernelError("moe_combine: float32 rows [T * top, D] and [T, D]")
-    if place is not None:
-        fn = _fn("grouped_gemm", "lq_moe_combine_at", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                                                       c_int, c_int, c_void_p])
-        _check(fn(_p(y), _p(place), _p(_contig(weights, "weights")), _p(shared), _p(shared_gate),
-                  shared_gate.stride(0) if shared_gate is not None else 0, _p(_contig(x, "x")), int(accumulate), T, top, D, _stream()),
-               "moe_combine")
-        return x
-    fn = _fn("grouped_gemm", "lq_moe_combine", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                                c_void_p])
-    _check(fn(_p(y), _p(_contig(weights, "weights")), _p(shared), _p(shared_gate),
-              shared_gate.stride(0) if shared_gate is not None else 0, _p(_contig(x, "x")), int(accumulate), T, top, D, _stream()),
-           "moe_combine")
+    if ids is not None and (h is None or h.dtype != torch.bfloat16 or tuple(h.shape) != (T, D) or not h.is_contiguous()
+                            or ids.dtype != torch.int32 or ids.numel() != T * top):
+        raise KernelError("moe_combine: ids int32 [T, top] come with the experts' input, contiguous bfloat16 [T, D]")
+    fn = _fn("grouped_gemm", "lq_moe_combine_more", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                     c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p])
+    _check(fn(_p(y), _p(place), _p(_contig(weights, "weights")), _p(shared), _p(shared_gate),
+              shared_gate.stride(0) if shared_gate is not None else 0, _p(_contig(x, "x")), int(accumulate), T, top, D,
+              _p(_contig(ids, "ids")) if ids is not None else None, int(E), _p(h) if ids is not None else None,
+              float(shared_scale), _stream()), "moe_combine")
     return x
 
 

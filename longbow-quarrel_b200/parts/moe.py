@@ -126,28 +126,37 @@ class RoutedExperts(FeedForward):
         shared = self.shared.forward(h, ctx, None) if self.shared is not None else None
         gate = z[:, self.routed] if self.shared is not None else None
         T = h.shape[0]
-        plain = not self.gated and not self.identity and scale == 1.0      # the form that the grouped products know
-        if plain and T * self.top >= self.TILED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
+        grouped = self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up)
+        # Identity outputs have no rows in the grouped products; the combination adds their tokens' own input instead.
+        more = dict(ids=ids, E=self.E, h=h) if self.identity else {}
+        if grouped and T * self.top >= self.TILED_FROM:
             # A prompt: the pairs in the order of their experts, every expert padded to whole row tiles, so that each
             # tile of the tcgen05 product reads one expert's weight; the second product reads the first one's rows as
             # they lie, and the combination finds each pair's row through the order's inverse.
             src, dst, tile_group = ops.group_rows_padded(ids.view(-1), self.E)
             u = ops.gemm_tc_grouped(ops.gather_rows(h, src, self.top), self.w_up, tile_group, h.dtype)
-            if self.activation is not None:
+            if self.gated:
+                u = ops.gated_act(u, None, self.activation, h.dtype)     # [rows, 2F] -> act(gate columns) * up columns
+            elif self.activation is not None:
                 ops.activation(u, self.activation, out=u)
             y = ops.gemm_tc_grouped(u, self.w_down, tile_group, torch.float32)
             out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
-            ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate, place=dst)
+            ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate, place=dst,
+                            shared_scale=scale, **more)
             return None if residual is not None else out
-        if plain and T * self.top >= self.GROUPED_FROM and self.F % 8 == 0 and ops.grouped_gemm_takes(h, self.w_up):
+        if grouped and T * self.top >= self.GROUPED_FROM:
             # Many tokens: the pairs sorted by expert (on the device), each expert's rows as tiles of a tensor-core product.
-            listed = ops.group_rows(ids.view(-1), self.E)
-            u = torch.empty((T * self.top, self.F), dtype=h.dtype, device=h.device)
-            ops.grouped_gemm(h, self.w_up, u, listed=listed, a_div=self.top, act=self.activation)
+            listed = ops.group_rows(ids.view(-1), self.routed)
+            n_up = self.w_up.shape[1]
+            u = torch.empty((T * self.top, n_up), dtype=h.dtype, device=h.device)
+            ops.grouped_gemm(h, self.w_up, u, listed=listed, a_div=self.top, act=None if self.gated else self.activation)
+            if self.gated:
+                u = ops.gated_act(u, None, self.activation, h.dtype)
             y = torch.empty((T * self.top, self.D), dtype=torch.float32, device=h.device)
             ops.grouped_gemm(u, self.w_down, y, listed=listed)
             out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
-            ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate)
+            ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate,
+                            shared_scale=scale, **more)
             return None if residual is not None else out
         u = ops.moe_up(h, self.w_up, ids, self.activation, gated=self.gated)
         more = dict(h=h if self.identity else None, shared_scale=scale)

@@ -77,7 +77,9 @@ def silu(z: torch.Tensor) -> torch.Tensor:
     return z * torch.sigmoid(z)
 
 
-def embed(tokens, table: torch.Tensor, bigram: torch.Tensor, hashing: dict) -> torch.Tensor:
+def embed(tokens, table: torch.Tensor, bigram: torch.Tensor | None, hashing: dict | None) -> torch.Tensor:
+    if hashing is None:
+        return torch.stack([table[int(tok)] for tok in tokens])
     n, a, b = int(hashing["buckets"]), int(hashing["mul_prev"]), int(hashing["mul_cur"])
     rows = []
     for t, tok in enumerate(tokens):
@@ -246,8 +248,9 @@ def forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, storage=None,
     global _STORAGE
     _STORAGE = storage
     try:
-        eps, m = float(cfg["norm"]["eps"]), float(cfg["residual_mult"])
-        x = embed(tokens, weights["embed"].to(dtype), weights["bigram"].to(dtype), cfg["embedding"]["bigram"])
+        eps, m = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
+        hashing = (cfg.get("embedding") or {}).get("bigram")
+        x = embed(tokens, weights["embed"].to(dtype), weights["bigram"].to(dtype) if hashing else None, hashing)
         kv = {}
         for i, layer in enumerate(cfg["layers"]):
             pre = f"l{i}."

@@ -39,6 +39,15 @@ def _close(got, ref, tol, rel=0.0):
     return err
 
 
+def _close_on_average(got, ref, tol):
+    """Rows that went through two roundings to bfloat16 on their way: the error's root mean square within `tol` of the
+    reference's, and no single element further off than ten times that."""
+    got, ref = got.float().cpu().double(), ref.float().cpu().double()
+    assert torch.isfinite(got).all()
+    rms = ref.pow(2).mean().sqrt().clamp_min(1e-30)
+    assert float((got - ref).pow(2).mean().sqrt() / rms) < tol and float((got - ref).abs().max() / rms) < 10 * tol
+
+
 # ------------------------------------------------------------------ a paged cache as a windowed sequence leaves it
 
 class Cache:
@@ -366,3 +375,179 @@ def test_causal_convolution_carries_its_last_rows_between_steps(dtype, taps, add
                 if s >= 0:
                     ref[t] += w[:, j].double().cpu() * h[s]
         _close(torch.cat(got[i]), ref, 2e-6 if dtype == torch.float32 else 1e-6, 0.0 if dtype == torch.float32 else BF16_ULP)
+
+
+# ------------------------------------------------------------------ rotation of a part of a head, value norm, cache write
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,hd,vd,rot,eps", [(4, 2, 16, 24, 8, 1e-5), (1, 1, 12, 20, 12, 1e-6), (3, 3, 8, 8, 0, 1e-2),
+                                               (8, 2, 64, 64, 48, 1e-5)])
+def test_rotation_value_norm_and_cache_write(dtype, H, G, hd, vd, rot, eps):
+    """Rows [q | k | v] of three sequences at scattered positions: the first `rot` dimensions of every query and key head
+    are rotated as halves (i, i + rot / 2) by the token's position, the rest pass; every value head is divided by its root
+    mean square; keys and values land in their pages at the token's place, and nothing else in the cache moves."""
+    ops = _ops()
+    page, n_pos = 64, 200
+    tok_seq, tok_pos = [0, 0, 0, 1, 2, 2], [0, 63, 64, 5, 130, 199]
+    slots = [2, 0, 1]
+    T, width = len(tok_pos), (H + G) * hd + G * vd
+    rows = _rand((T, width), dtype, 20)
+    freqs = torch.tensor([50.0 ** (-2.0 * i / max(rot, 2)) for i in range(rot // 2)], dtype=torch.float64)
+    ang = torch.arange(n_pos, dtype=torch.float64)[:, None] * freqs
+    cos, sin = torch.cos(ang).float().to(DEV).contiguous(), torch.sin(ang).float().to(DEV).contiguous()
+    table = torch.full((3, 4), -1, dtype=torch.int32)
+    nxt = 0
+    for s, p in zip(tok_seq, tok_pos):
+        if table[slots[s], p // page] < 0:
+            table[slots[s], p // page] = nxt
+            nxt += 1
+    table = table.to(DEV)
+    k_pages = torch.full((nxt, G, page, hd), 9.0, dtype=dtype, device=DEV)
+    v_pages = torch.full((nxt, G, page, vd), 9.0, dtype=dtype, device=DEV)
+    src = rows.double().cpu()
+    buf = rows.clone()
+    ops.rope_partial(buf, None, cos if rot else None, sin if rot else None, rot, _i32(tok_pos), _i32(tok_seq), _i32(slots), table,
+                     k_pages, v_pages, H + G, H, G, hd, vd, (H + G) * hd, page, v_unit_eps=eps)
+    tol, rel = (2e-6, 0.0) if dtype == torch.float32 else (1e-6, BF16_ULP)
+    written = 0
+    for r, (s, p) in enumerate(zip(tok_seq, tok_pos)):
+        heads = src[r, :(H + G) * hd].reshape(H + G, hd).clone()
+        a, b = heads[:, :rot // 2].clone(), heads[:, rot // 2:rot].clone()
+        c, sn = torch.cos(ang[p]), torch.sin(ang[p])
+        heads[:, :rot // 2], heads[:, rot // 2:rot] = a * c - b * sn, b * c + a * sn
+        _close(buf[r, :H * hd].reshape(H, hd), heads[:H], tol, rel)
+        pg = int(table[slots[s], p // page])
+        _close(k_pages[pg, :, p % page], heads[H:], tol, rel)
+        v = src[r, (H + G) * hd:].reshape(G, vd)
+        _close(v_pages[pg, :, p % page], v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps), tol, rel)
+        written += 1
+    assert int((k_pages != 9.0).any(-1).sum()) <= written * G and int((v_pages != 9.0).any(-1).sum()) <= written * G
+
+
+# ------------------------------------------------------------------ the router
+
+def _route_ref(z, corr, groups, keep, top):
+    """Softmax scores; the choice by score + correction inside the `keep` groups whose best choice score is largest;
+    the weights are the chosen plain scores.  Returns (chosen, weights, margin to the nearest other outcome)."""
+    s = torch.softmax(z.double(), 0)
+    c = (s + corr.double()).tolist()
+    n = len(c)
+    per = n // groups
+    gs = [max(c[g * per:(g + 1) * per]) for g in range(groups)]
+    order = sorted(range(groups), key=lambda g: (-gs[g], g))
+    kept = set(order[:keep])
+    allowed = sorted((e for e in range(n) if e // per in kept), key=lambda e: (-c[e], e))
+    margin = gs[order[keep - 1]] - gs[order[keep]] if keep < groups else math.inf
+    if len(allowed) > top:
+        margin = min(margin, c[allowed[top - 1]] - c[allowed[top]])
+    return allowed[:top], [float(s[e]) for e in allowed[:top]], margin
+
+
+@pytest.mark.parametrize("n,groups,keep,top", [(12, 4, 3, 4), (8, 4, 2, 3), (6, 1, 1, 2), (16, 4, 1, 4), (4, 2, 2, 4), (5, 5, 2, 1),
+                                               (64, 8, 4, 8)])
+def test_router_softmax_correction_and_groups_by_their_best_member(n, groups, keep, top):
+    """300 tokens: the chosen set equals the float64 rule wherever that rule's decision is not a close call; the weights are
+    the plain softmax scores times the scale, in the order of the choice scores; corrections include negative ones large
+    enough that every choice score of some kept group is below zero."""
+    ops = _ops()
+    T = 300
+    z = _rand((T, n + 1), torch.float32, 30, scale=2.0)                 # one more column rides along, as the shared gate does
+    corr = _rand((n,), torch.float32, 31, scale=0.3) - 0.4
+    ids, weights = ops.moe_route(z, n, groups, keep, top, 0.5, score="softmax", correction=corr, group_rule="max", normalize=False)
+    ids, weights = ids.cpu(), weights.cpu()
+    firm = 0
+    for t in range(T):
+        chosen, w, margin = _route_ref(z[t, :n].cpu(), corr.cpu(), groups, keep, top)
+        if margin < 1e-5:
+            continue
+        firm += 1
+        assert ids[t].tolist() == chosen, (t, ids[t].tolist(), chosen)
+        assert np.allclose(weights[t].numpy(), 0.5 * np.asarray(w), rtol=2e-6, atol=1e-9)
+    assert firm > 250
+    plain_ids, plain_w = ops.moe_route(z, n, groups, keep, top, 1.0, score="softmax", group_rule="max", normalize=False)
+    for t in range(0, T, 7):
+        chosen, w, margin = _route_ref(z[t, :n].cpu(), torch.zeros(n), groups, keep, top)
+        if margin >= 1e-5:
+            assert plain_ids[t].tolist() == chosen and np.allclose(plain_w[t].cpu().numpy(), w, rtol=2e-6)
+
+
+# ------------------------------------------------------------------ gated experts, identity experts, the multiplier
+
+def _experts_ref(h, w_up, w_down, ids, weights, E, shared, zs, shared_scale):
+    """float64: sum over the chosen of weight * (W_down (silu(W_gate h) * (W_up h))), or weight * h for an identity
+    expert; plus shared_scale * sigmoid(zs) * shared."""
+    T, D = h.shape
+    F = w_up.shape[1] // 2
+    out = torch.zeros((T, D), dtype=torch.float64)
+    for t in range(T):
+        x = h[t].double().cpu()
+        for e, w in zip(ids[t].tolist(), weights[t].tolist()):
+            if e >= E:
+                out[t] += w * x
+                continue
+            gu = w_up[e].double().cpu() @ x
+            u = torch.nn.functional.silu(gu[:F]) * gu[F:]
+            u = u.to(h.dtype).double()                                    # the products hand their rows on in the rows' dtype
+            out[t] += w * (w_down[e].double().cpu() @ u)
+        if shared is not None:
+            out[t] += shared_scale * torch.sigmoid(zs[t].double().cpu()) * shared[t].double().cpu()
+    return out
+
+
+def _expert_case(T, D, F, E, identity, top, dtype, seed):
+    rng = np.random.default_rng(seed)
+    h = _rand((T, D), dtype, seed)
+    w_up = _rand((E, 2 * F, D), dtype, seed + 1, scale=D ** -0.5)
+    w_down = _rand((E, D, F), dtype, seed + 2, scale=F ** -0.5)
+    ids = torch.tensor(np.stack([rng.permutation(E + identity)[:top] for _ in range(T)]), dtype=torch.int32, device=DEV)
+    weights = torch.rand((T, top), device=DEV, dtype=torch.float32) * 0.5
+    shared = _rand((T, D), torch.float32, seed + 3)
+    zs = _rand((T, 3), torch.float32, seed + 4)[:, 1]                     # a strided column, as the router's product leaves it
+    return h, w_up, w_down, ids, weights, shared, zs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,D,F,E,identity,top", [(1, 64, 32, 6, 2, 3), (5, 40, 16, 1, 3, 4), (16, 128, 48, 13, 3, 4), (3, 100, 24, 3, 0, 3)])
+def test_streamed_gated_experts_pass_identity_inputs_on(dtype, T, D, F, E, identity, top):
+    ops = _ops()
+    h, w_up, w_down, ids, weights, shared, zs = _expert_case(T, D, F, E, identity, top, dtype, 40)
+    ref = _experts_ref(h, w_up, w_down, ids, weights, E, shared, zs, 0.7)
+    x0 = _rand((T, D), torch.float32, 49)
+    u = ops.moe_up(h, w_up, ids, "silu", gated=True)
+    for accumulate in (False, True):
+        x = x0.clone()
+        ops.moe_down(u, w_down, ids, weights, x, accumulate=accumulate, shared=shared, shared_gate=zs,
+                     h=h if identity else None, shared_scale=0.7)
+        want = ref + (x0.double().cpu() if accumulate else 0.0)
+        _close(x, want, 5e-6 if dtype == torch.float32 else 4e-3)
+
+
+@pytest.mark.parametrize("T,D,F,E,identity,top", [(700, 128, 48, 13, 3, 4), (300, 64, 32, 6, 2, 3), (520, 256, 64, 2, 2, 1)])
+def test_grouped_gated_experts_leave_identity_pairs_out_of_the_products(T, D, F, E, identity, top):
+    """A prompt's (token, choice) pairs through both grouped forms -- row tiles of the tcgen05 product padded per expert,
+    and the listed mma.sync product -- against float64: pairs that chose an identity output take no place in the padded
+    order, have no tile, and come back as the token's own input times the weight."""
+    ops = _ops()
+    h, w_up, w_down, ids, weights, shared, zs = _expert_case(T, D, F, E, identity, top, torch.bfloat16, 50)
+    ref = _experts_ref(h, w_up, w_down, ids, weights, E, shared, zs, 0.5)
+    more = dict(ids=ids, E=E, h=h) if identity else {}
+    src, dst, tile_group = ops.group_rows_padded(ids.view(-1), E)
+    flat, place = ids.view(-1).cpu(), dst.cpu()
+    assert ((place < 0) == (flat >= E)).all() and len(set(place[place >= 0].tolist())) == int((flat < E).sum())
+    groups = tile_group.cpu()
+    assert all(int(groups[int(p) // 128]) == int(e) for p, e in zip(place.tolist(), flat.tolist()) if p >= 0)
+    u = ops.gemm_tc_grouped(ops.gather_rows(h, src, top), w_up, tile_group, h.dtype)
+    y = ops.gemm_tc_grouped(ops.gated_act(u, None, "silu", h.dtype), w_down, tile_group, torch.float32)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_status() == 0
+    out = ops.moe_combine(y, weights, torch.empty((T, D), dtype=torch.float32, device=DEV), accumulate=False, shared=shared,
+                          shared_gate=zs, place=dst, shared_scale=0.5, **more)
+    _close_on_average(out, ref, 4e-3)
+    listed = ops.group_rows(ids.view(-1), E + identity)
+    u = torch.empty((T * top, 2 * F), dtype=h.dtype, device=DEV)
+    ops.grouped_gemm(h, w_up, u, listed=listed, a_div=top)
+    y = torch.full((T * top, D), float("nan"), dtype=torch.float32, device=DEV)
+    ops.grouped_gemm(ops.gated_act(u, None, "silu", h.dtype), w_down, y, listed=listed)
+    x0 = _rand((T, D), torch.float32, 59)
+    out = ops.moe_combine(y, weights, x0.clone(), accumulate=True, shared=shared, shared_gate=zs, shared_scale=0.5, **more)
+    _close_on_average(out, ref + x0.double().cpu(), 4e-3)
