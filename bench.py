@@ -347,6 +347,24 @@ def zoporax_config(size: str, window: int, groups: int = 1) -> dict:
             "max_positions": 8192}
 
 
+def raritar_config(size: str, window: int) -> dict:
+    """Four layers of attention (capped scores, a window with kept first positions, rotation of half of each head with
+    rescaled frequencies, normed values; the last layer on the first one's keys and values) behind a causal convolution,
+    each with routed gated experts (62 and two identity outputs in eight groups of which three are kept, six per token) and
+    a shared expert; pair-hash embedding; branch multiplier."""
+    width, heads, kv, dim, _ = DESIGN_SIZES[size]
+    experts, top, eff, sff = ZOPORAX_SIZES[size][8:12]
+    att = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+           "mask": {"size": window, "keep_first": 4},
+           "rot": {"dims": dim // 2, "base": 5e5, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": sff},
+           "router": {"experts": experts - 2, "identity": 2, "top": top, "groups": {"count": 8, "keep": 3}}}
+    layers = [{"type": "attention", "mixer": dict(att, **({"kv_from": 0} if i == 3 else {})), "mlp": moe} for i in range(4)]
+    return {"architecture": "Raritar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "canon": {"taps": 4}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": layers, "max_positions": 8192}
+
+
 def _kernel_times(torch, run, warm: int = 2) -> tuple[dict, float]:
     """What every kind of kernel adds to the device time of one call of run(): {kind: (launches, total us)}, and the span."""
     import re
@@ -378,6 +396,8 @@ def _kernel_times(torch, run, warm: int = 2) -> tuple[dict, float]:
 def design_bench(args) -> int:
     if args.design == "zoporax":
         return zoporax_bench(args)
+    if args.design == "raritar":
+        return raritar_bench(args)
     return fetorax_bench(args)
 
 
@@ -507,6 +527,140 @@ def zoporax_bench(args) -> int:
     return 0
 
 
+def _expert_products_us(torch, T, B, width, experts, identity, top, eff, gated, K) -> dict:
+    """Device time of the experts' products alone at one layer's sizes, random routing: the prompt's two row-tiled tcgen05
+    products (with the gather ahead of them, the activation between them and the combination behind them) for T tokens,
+    and the two streaming kernels for B single tokens.  Every launch reads other weights than fit in L2 beside the one
+    before it (several hundred MB of experts), so nothing is flushed."""
+    from longbow_quarrel_b200.kernels import ops
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(1)
+    n_up = 2 * eff if gated else eff
+    w_up = torch.randn((experts, n_up, width), device=dev, dtype=torch.bfloat16, generator=g) * width ** -0.5     # gated: gate and up rows by turns
+    w_down = torch.randn((experts, width, eff), device=dev, dtype=torch.bfloat16, generator=g) * eff ** -0.5
+    act = "silu"
+
+    def case(rows):
+        h = torch.randn((rows, width), device=dev, dtype=torch.bfloat16, generator=g)
+        ids = torch.stack([torch.randperm(experts + identity, device=dev, generator=g)[:top] for _ in range(rows)]).to(torch.int32)
+        weights = torch.rand((rows, top), device=dev, generator=g)
+        return h, ids.contiguous(), weights, torch.zeros((rows, width), device=dev, dtype=torch.float32)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        a, b = events(torch)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(K):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / K * 1e3
+    out = {}
+    h, ids, weights, x = case(T)
+    more = dict(ids=ids, E=experts, h=h) if identity else {}
+    src, dst, tile_group = ops.group_rows_padded(ids.view(-1), experts)
+    rows = ops.gather_rows(h, src, top)
+    out["prompt_first_product"] = timed(lambda: ops.gemm_tc_grouped(rows, w_up, tile_group, h.dtype, swiglu=gated))
+    u = ops.gemm_tc_grouped(rows, w_up, tile_group, h.dtype, swiglu=gated)
+    if not gated:
+        ops.activation(u, act, out=u)
+    out["prompt_second_product"] = timed(lambda: ops.gemm_tc_grouped(u, w_down, tile_group, torch.float32))
+    y = ops.gemm_tc_grouped(u, w_down, tile_group, torch.float32)
+
+    def around():
+        s2, d2, _ = ops.group_rows_padded(ids.view(-1), experts)
+        r2 = ops.gather_rows(h, s2, top)
+        if not gated:
+            ops.activation(torch.empty((r2.shape[0], n_up), device=dev, dtype=h.dtype), act)
+        ops.moe_combine(y, weights, x, accumulate=True, place=d2, **more)
+    out["prompt_order_gather_activation_combination"] = timed(around)
+    h, ids, weights, x = case(B)
+    out["single_tokens_first_product"] = timed(lambda: ops.moe_up(h, w_up, ids, act, gated=gated, block=8 if gated else 0))
+    u = ops.moe_up(h, w_up, ids, act, gated=gated, block=8 if gated else 0)
+    out["single_tokens_second_product"] = timed(lambda: ops.moe_down(u, w_down, ids, weights, x, accumulate=True,
+                                                                     h=h if identity else None))
+    del w_up, w_down
+    torch.cuda.empty_cache()
+    return {k: round(v, 1) for k, v in out.items()}
+
+
+def raritar_bench(args) -> int:
+    """Prefill and decode of a Raritar model of realistic layer sizes beside the closest model the library has, a Llama
+    model of the same width, depth, heads and head size (random weights, vocabulary 32,000, the window longer than the
+    context so that both attend to every key): tokens a second, what every kind of kernel adds to a prompt step and to a
+    decode step, and how many times their roofline the design's kernels take beside the like kernels: attention beside
+    Llama's attention, and the gated experts' products beside the ungated ones of equal sizes as the Zoporax design runs them."""
+    import numpy as np
+    import torch
+
+    from longbow_quarrel_b200.engine import Engine
+    peaks, peaks_from = load_peaks()
+    K, W = args.steps, max(3, args.warmup)
+    T, B, ctx = PREFILL_TOKENS, BATCH, 2048
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {}
+    for size in args.sizes.split(","):
+        width, heads, kv, dim, ff = DESIGN_SIZES[size]
+        experts, top, eff, sff = ZOPORAX_SIZES[size][8:12]
+        configs = {"raritar": raritar_config(size, ctx + 256),
+                   "llama": dict(llama(width, 4, heads, kv, dim, ff, 8.0, False), vocab_size=DESIGN_VOCAB, max_position_embeddings=8192)}
+        res = {name: _design_run(torch, np, Engine, cfg, name, T, B, ctx, K, W, rng) for name, cfg in configs.items()}
+        gated = _expert_products_us(torch, T, B, width, experts - 2, 2, top, eff, True, max(5, K // 4))
+        plain = _expert_products_us(torch, T, B, width, experts, 0, top, eff, False, max(5, K // 4))
+
+        def per_launch(kinds, *names):
+            n = sum(kinds[k][0] for k in names if k in kinds)
+            return sum(kinds[k][1] for k in names if k in kinds) / n if n else None
+
+        def times(us, nbytes, flops):
+            return round(us / (max(nbytes / hbm, flops / tensor) * 1e6), 2) if us else None
+        r, l = res["raritar"], res["llama"]
+        qkv_bytes = T * heads * 3 * dim * 2.0
+        att_flops = 4.0 * heads * dim * T * (T + 1) / 2
+        kv_read = B * ctx * 2 * kv * dim * 2.0
+        real = top * (experts - 2) / experts                       # of a token's choices, those with matrices of their own
+
+        def expert_rows(us, n_up, share, hit):
+            """times the roofline: first product, second product of a prompt; first, second of single tokens."""
+            w1, w2 = n_up * width * 2.0, eff * width * 2.0
+            return {"prompt, first product": times(us["prompt_first_product"], hit * w1 + T * share * (width + n_up) * 2.0,
+                                                   2.0 * T * share * n_up * width),
+                    "prompt, second product": times(us["prompt_second_product"], hit * w2 + T * share * (eff * 2.0 + width * 4.0),
+                                                    2.0 * T * share * eff * width),
+                    "single tokens, first product": times(us["single_tokens_first_product"], min(B * share, hit) * w1, 0.0),
+                    "single tokens, second product": times(us["single_tokens_second_product"], min(B * share, hit) * w2, 0.0)}
+        roof = {
+            "prefill": {
+                "llama attention": times(per_launch(l["prefill_kernels_us"], "attn_prefill_two", "attn_prefill_tc", "attn_prefill"),
+                                         qkv_bytes, att_flops),
+                "raritar attention (capped, window, kept first)": times(
+                    per_launch(r["prefill_kernels_us"], "attn_prefill_two", "attn_prefill_tc", "attn_prefill"), qkv_bytes, att_flops),
+            },
+            "decode": {
+                "llama attention": times(per_launch(l["decode_kernels_us"], "attn_decode"), kv_read, 0.0),
+                "raritar attention (capped, window, kept first)": times(per_launch(r["decode_kernels_us"], "attn_decode"), kv_read, 0.0),
+            },
+            "raritar gated experts": expert_rows(gated, 2 * eff, real, experts - 2),
+            "ungated experts of equal sizes": expert_rows(plain, eff, top, experts),
+        }
+        out[size] = {"raritar": r, "llama": l, "expert_products_us": {"raritar gated": gated, "ungated": plain},
+                     "times_the_roofline": roof,
+                     "raritar_over_llama": {"prefill": round(r["prefill_tokens_per_s"] / l["prefill_tokens_per_s"], 3),
+                                            "decode": round(r["decode_tokens_per_s"] / l["decode_tokens_per_s"], 3)}}
+    clocks = sampler.stop()
+    print(json.dumps({"design": "raritar", "beside": "llama", "dtype": "bf16", "data": "synthetic", "layers": 4,
+                      "layer_order": "attention + routed gated experts four times, the last on the first layer's keys and values; "
+                                     "beside attention + gated feed-forward four times",
+                      "vocab": DESIGN_VOCAB, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx, "steps": K,
+                      "warmup": W, "peaks": peaks, "peaks_from": peaks_from, "clocks": clocks, "sizes": out}))
+    return 0
+
+
 def fetorax_bench(args) -> int:
     """Prefill and decode of a Fetorax model of the 1B and 8B layer sizes beside a Llama model of the same sizes
     (random weights, vocabulary cut to 32,000): tokens a second, the device time of every kind of kernel in one
@@ -616,9 +770,9 @@ def fetorax_bench(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default="", choices=["", "fetorax", "zoporax"],
+    ap.add_argument("--design", default="", choices=["", "fetorax", "zoporax", "raritar"],
                     help="instead of the default workload: this design beside the closest model the library has, at equal layer "
-                         "sizes (prefill, decode, kernel by kernel): fetorax beside Llama, zoporax beside Fetorax")
+                         "sizes (prefill, decode, kernel by kernel): fetorax beside Llama, zoporax beside Fetorax, raritar beside Llama")
     ap.add_argument("--sizes", default="1b,8b", help="--design: layer sizes to run, of " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)

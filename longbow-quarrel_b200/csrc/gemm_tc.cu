@@ -550,16 +550,19 @@ LQ_EXPORT int lq_gemm_tc_qkv(const void* X, const void* W, void* q_out, int M, i
 
 // Many products in one launch: the rows of A [M, K] come in tiles of 128 that each belong to one group (tile_group
 // [M / 128] on the device: the group, or -1 for a tile to leave out), and a tile of group g is multiplied with rows
-// g * N .. (g + 1) * N of W [G * N, K].  C [M, N] bfloat16 (out_f32 0) or float32 (1).  M a multiple of 128.
+// g * N .. (g + 1) * N of W [G * N, K].  C [M, N] bfloat16 (out_f32 0) or float32 (1); out_f32 2: every group's rows are
+// 8 gate rows and 8 up rows by turns (N a multiple of 16) and C is [M, N / 2] bfloat16, silu(gate) * up.  M a multiple of 128.
 LQ_EXPORT int lq_gemm_tc_grouped(const void* A, const void* W, void* C, int out_f32, int M, int N, int K, int G,
                                  const int* tile_group, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || G <= 0) return LQ_OK;
     if (M % BM || K <= 0 || K % 8 || !tile_group || (((uintptr_t)A | (uintptr_t)W) & 15)) return LQ_BAD_SIZE;
+    if (out_f32 < 0 || out_f32 > 2 || (out_f32 == 2 && N % 16)) return LQ_BAD_SIZE;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, M, K, BM);
     if (rc != LQ_OK) return rc;
     rc = make_map(&mb, W, G * N, K, 256);
     if (rc != LQ_OK) return rc;
+    if (out_f32 == 2) return launch_epi<256, 4, EPI_SWIGLU, BM>(ma, mb, C, nullptr, M, N, K, sm_count(), 1, QkvArgs{}, stream, tile_group);
     if (out_f32) return launch_epi<256, 4, EPI_F32, BM>(ma, mb, C, nullptr, M, N, K, sm_count(), 1, QkvArgs{}, stream, tile_group);
     return launch_epi<256, 4, EPI_BF16, BM>(ma, mb, C, nullptr, M, N, K, sm_count(), 1, QkvArgs{}, stream, tile_group);
 }

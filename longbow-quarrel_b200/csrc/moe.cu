@@ -161,7 +161,7 @@ constexpr int MX_PER_WARP = 4;        // output rows a warp makes one after the 
 template <typename T>
 __global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up,
                                                                const int* __restrict__ ids, T* __restrict__ u, int top, int D,
-                                                               int F, int act, int gated, int n_real) {
+                                                               int F, int act, int gated, int n_real, int block) {
     pdl_launch_dependents();
     extern __shared__ __align__(16) float xs[];   // [D]
     const int pair = blockIdx.x, t = pair / top, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -170,19 +170,23 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_up_kernel(const T* __restri
     const int e = ids[pair];
     if (e >= n_real) return;                       // an identity expert has no matrices: its output is the input itself
     __syncthreads();
-    const T* w = w_up + (size_t)e * (gated ? 2 : 1) * F * D;     // gated: F gate rows, then F up rows
+    const T* w = w_up + (size_t)e * (gated ? 2 : 1) * F * D;     // gated: F gate rows, then F up rows (block 0) ...
+    // ... or `block` gate rows and the `block` up rows that go with them by turns (the layout whose product the
+    // tensor-core kernels' gated epilogue reads)
+    auto gate_row = [&](int f) { return block ? (size_t)(f / block) * 2 * block + f % block : (size_t)f; };
+    const size_t up_after = block ? (size_t)block : (size_t)F;
     // The lanes' shares of all the warp's outputs first (their loads are in flight together), then the sums.
     float part[MX_PER_WARP];
 #pragma unroll
     for (int i = 0; i < MX_PER_WARP; ++i) {
         const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
-        part[i] = f < F ? row_part(xs, w + (size_t)f * D, D, lane) : 0.f;
+        part[i] = f < F ? row_part(xs, w + (gated ? gate_row(f) : (size_t)f) * D, D, lane) : 0.f;
     }
     float part_up[MX_PER_WARP];
 #pragma unroll
     for (int i = 0; i < MX_PER_WARP; ++i) {
         const int f = (blockIdx.y * MX_PER_WARP + i) * MX_WARPS + warp;
-        part_up[i] = (gated && f < F) ? row_part(xs, w + (size_t)(F + f) * D, D, lane) : 0.f;
+        part_up[i] = (gated && f < F) ? row_part(xs, w + (gate_row(f) + up_after) * D, D, lane) : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < MX_PER_WARP; ++i) {
@@ -236,19 +240,26 @@ __global__ void __launch_bounds__(MX_WARPS * 32) moe_down_kernel(const T* __rest
     }
 }
 
-LQ_EXPORT int lq_moe_up(const void* h, const void* w_up, const int* ids, void* u, int dtype, int T, int top, int D, int F, int act,
-                        int gated, int n_real, cudaStream_t stream) {
+// block (gated only): 0 = an expert's F gate rows, then its F up rows; b > 0 (F a multiple of b) = b gate rows and b up rows by turns.
+LQ_EXPORT int lq_moe_up_rows(const void* h, const void* w_up, const int* ids, void* u, int dtype, int T, int top, int D, int F, int act,
+                             int gated, int n_real, int block, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (act < 0 || act > 4 || (size_t)D * 4 > 200 * 1024) return LQ_BAD_SIZE;
+    if (block < 0 || (block && (!gated || F % block))) return LQ_BAD_SIZE;
     dim3 grid(T * top, (F + MX_WARPS * MX_PER_WARP - 1) / (MX_WARPS * MX_PER_WARP));
     const size_t smem = (size_t)D * sizeof(float);
     typedef __nv_bfloat16 bf;
 #define LQ_GO(TT) do { if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        return launch_pdl(moe_up_kernel<TT>, grid, dim3(MX_WARPS * 32), smem, stream, (const TT*)h, (const TT*)w_up, ids, (TT*)u, top, D, F, act, gated, n_real); } while (0)
+        return launch_pdl(moe_up_kernel<TT>, grid, dim3(MX_WARPS * 32), smem, stream, (const TT*)h, (const TT*)w_up, ids, (TT*)u, top, D, F, act, gated, n_real, block); } while (0)
     if (dtype == LQ_F32) LQ_GO(float);
     if (dtype == LQ_BF16) LQ_GO(bf);
 #undef LQ_GO
     return LQ_BAD_DTYPE;
+}
+
+LQ_EXPORT int lq_moe_up(const void* h, const void* w_up, const int* ids, void* u, int dtype, int T, int top, int D, int F, int act,
+                        int gated, int n_real, cudaStream_t stream) {
+    return lq_moe_up_rows(h, w_up, ids, u, dtype, T, top, D, F, act, gated, n_real, 0, stream);
 }
 
 LQ_EXPORT int lq_moe_down(const void* u, const void* w_down, const int* ids, const float* weights, const float* shared,

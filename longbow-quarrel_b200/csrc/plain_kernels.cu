@@ -121,6 +121,56 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
     }
 }
 
+// The same sums for rows whose channels come in whole 16-byte pieces: a thread makes 16 / sizeof(T) neighbouring channels,
+// every tap's piece one load, the taps added in the same order as above.
+template <typename T>
+__global__ void __launch_bounds__(256) causal_conv_vec_kernel(const T* __restrict__ h, T* __restrict__ out, const float* __restrict__ w,
+                                                              const float* __restrict__ state, const int* __restrict__ tok_seq,
+                                                              const int* __restrict__ slots, const int* __restrict__ cu_rows, int D,
+                                                              int taps, int add_input) {
+    constexpr int V = 16 / sizeof(T);
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, b = tok_seq[t], first = cu_rows[b], i = t - first, keep = taps - 1;
+    const int d = (blockIdx.y * 256 + threadIdx.x) * V;
+    if (d >= D) return;
+    const float* st = state + (size_t)slots[b] * keep * D;
+    auto piece = [&](const T* p, float (&v)[V]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int c = 0; c < V; ++c) v[c] = to_f32(e[c]);
+    };
+    float own[V], acc[V];
+    piece(h + (size_t)t * D + d, own);
+#pragma unroll
+    for (int c = 0; c < V; ++c) acc[c] = 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int k = i - keep + j;
+        float v[V];
+        if (j == keep) {
+#pragma unroll
+            for (int c = 0; c < V; ++c) v[c] = own[c];
+        } else if (k >= 0) {
+            piece(h + (size_t)(first + k) * D + d, v);
+        } else {
+            const float4* sp = reinterpret_cast<const float4*>(st + (size_t)(keep + k) * D + d);
+#pragma unroll
+            for (int c = 0; c < V / 4; ++c) {
+                const float4 f = sp[c];
+                v[4 * c] = f.x; v[4 * c + 1] = f.y; v[4 * c + 2] = f.z; v[4 * c + 3] = f.w;
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < V; ++c) acc[c] = fmaf(w[(size_t)(d + c) * taps + j], v[c], acc[c]);
+    }
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int c = 0; c < V; ++c) e[c] = from_f32<T>(add_input ? own[c] + acc[c] : acc[c]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * D + d) = raw;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) conv_state_kernel(const T* __restrict__ h, float* __restrict__ state,
                                                          const int* __restrict__ slots, const int* __restrict__ cu_rows, int D,
@@ -143,7 +193,14 @@ LQ_EXPORT int lq_causal_conv(const void* h, void* out, int dtype, const float* w
     const int ny = (D + 1023) / 1024;
     int rc;
     typedef __nv_bfloat16 bf;
-    if (dtype == LQ_F32)
+    const bool pieces = (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
+    if (dtype == LQ_F32 && pieces && D % 4 == 0)
+        rc = launch_pdl(causal_conv_vec_kernel<float>, dim3(T, (D / 4 + 255) / 256), dim3(256), 0, stream, (const float*)h, (float*)out,
+                        w, (const float*)state, tok_seq, slots, cu_rows, D, taps, add_input);
+    else if (dtype == LQ_BF16 && pieces && D % 8 == 0)
+        rc = launch_pdl(causal_conv_vec_kernel<bf>, dim3(T, (D / 8 + 255) / 256), dim3(256), 0, stream, (const bf*)h, (bf*)out, w,
+                        (const float*)state, tok_seq, slots, cu_rows, D, taps, add_input);
+    else if (dtype == LQ_F32)
         rc = launch_pdl(causal_conv_kernel<float>, dim3(T, ny), dim3(256), 0, stream, (const float*)h, (float*)out, w, (const float*)state,
                         tok_seq, slots, cu_rows, D, taps, add_input);
     else if (dtype == LQ_BF16)
@@ -165,8 +222,22 @@ __global__ void add_scaled_kernel(float* __restrict__ x, const float* __restrict
     if (i < total) x[i] = fmaf(m, y[i], x[i]);
 }
 
+__global__ void add_scaled4_kernel(float4* __restrict__ x, const float4* __restrict__ y, float m, size_t total4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    float4 a = x[i];
+    const float4 b = y[i];
+    a.x = fmaf(m, b.x, a.x); a.y = fmaf(m, b.y, a.y); a.z = fmaf(m, b.z, a.z); a.w = fmaf(m, b.w, a.w);
+    x[i] = a;
+}
+
 LQ_EXPORT int lq_add_scaled(float* x, const float* y, float m, long long total, cudaStream_t stream) {
     if (total <= 0) return LQ_OK;
+    if (total % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0)
+        return launch_pdl(add_scaled4_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (float4*)x, (const float4*)y, m,
+                          (size_t)(total / 4));
     return launch_pdl(add_scaled_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, y, m, (size_t)total);
 }
 

@@ -635,18 +635,23 @@ def gather_rows(a: torch.Tensor, src: torch.Tensor, div: int = 1) -> torch.Tenso
     return out
 
 
-def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out_dtype: torch.dtype,
+                    swiglu: bool = False) -> torch.Tensor:
     """a [M, K] (M a multiple of 128, its row tiles each of one group) times w [G, N, K]: row tile i is multiplied with
     w[tile_group[i]] on the tcgen05 tensor cores (tiles with group -1 are left out and their rows of the result are not
-    written).  Returns [M, N] in out_dtype (bfloat16 or float32)."""
+    written).  Returns [M, N] in out_dtype (bfloat16 or float32).  swiglu: every group's rows are 8 gate rows and 8 up
+    rows by turns (`linear.interleave_gate_up`), and what comes back is silu(gate) * up, [M, N / 2] bfloat16."""
     M, K = a.shape
     G, N, K2 = w.shape
+    if swiglu and (N % 16 or out_dtype != torch.bfloat16):
+        raise KernelError("gemm_tc_grouped: the gated form takes 16 rows of weight at a time and hands on bfloat16")
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K2 != K or K % 8 or M % GROUP_TILE or not a.is_contiguous() \
             or not w.is_contiguous() or tile_group.numel() != M // GROUP_TILE:
         raise KernelError("gemm_tc_grouped: contiguous bfloat16 operands, K a multiple of 8, whole row tiles with a group each")
-    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=a.device)
     fn = _fn("gemm_tc", "lq_gemm_tc_grouped", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(_p(a), _p(w), _p(out), int(out_dtype == torch.float32), M, N, K, G, _p(tile_group), _stream()), "gemm_tc_grouped")
+    _check(fn(_p(a), _p(w), _p(out), 2 if swiglu else int(out_dtype == torch.float32), M, N, K, G, _p(tile_group), _stream()),
+           "gemm_tc_grouped")
     return out
 
 
@@ -703,10 +708,12 @@ def moe_route(z: torch.Tensor, E: int, groups: int, keep: int, top: int, scale: 
     return ids, weights
 
 
-def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: str | None, gated: bool = False) -> torch.Tensor:
+def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: str | None, gated: bool = False,
+           block: int = 0) -> torch.Tensor:
     """u[t, j] = act(w_up[ids[t, j]] h[t]) for w_up [E, F, D]; returns [T, top, F] in h's dtype.  gated: w_up is
-    [E, 2F, D], an expert's F gate rows ahead of its F up rows, and u = act(gate rows . h) * (up rows . h).  Chosen
-    experts numbered E and above (identity experts) have no rows; their u is left unwritten."""
+    [E, 2F, D], an expert's F gate rows ahead of its F up rows (or, with `block` b, b gate rows and b up rows by turns),
+    and u = act(gate rows . h) * (up rows . h).  Chosen experts numbered E and above (identity experts) have no rows;
+    their u is left unwritten."""
     T, D = h.shape
     E, F, D2 = w_up.shape
     if gated:
@@ -715,10 +722,10 @@ def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, act: str | No
         raise KernelError("moe_up: a contiguous weight [E, F, D] of the rows' dtype")
     top = ids.shape[1]
     u = torch.empty((T, top, F), dtype=h.dtype, device=h.device)
-    fn = _fn("moe", "lq_moe_up", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_void_p])
-    _check(fn(_p(_contig(h, "h")), _p(w_up), _p(ids), _p(u), dtype_code(h), T, top, D, F, MOE_ACTS[act], int(gated), E, _stream()),
-           "moe_up")
+    fn = _fn("moe", "lq_moe_up_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_int, c_void_p])
+    _check(fn(_p(_contig(h, "h")), _p(w_up), _p(ids), _p(u), dtype_code(h), T, top, D, F, MOE_ACTS[act], int(gated), E, int(block),
+              _stream()), "moe_up")
     return u
 
 

@@ -28,7 +28,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import linear, ops
 from ..weights.spec import WeightSpec
 from .base import FeedForward, Runtime, StepContext
 from .registry import make_part, register_part
@@ -81,6 +81,7 @@ class RoutedExperts(FeedForward):
                     "hidden_size": hidden_size, "intermediate_size": shared_size, "activation": shared_activation or activation,
                     "names": {"up": f"{n['shared']}.{n['up']}", "down": f"{n['shared']}.{n['down']}"}}), runtime)
         self.w_route = self.w_up = self.w_down = self.correction = None
+        self.up_block = 0        # gated: how an expert's gate and up rows lie in w_up (see load)
 
     takes_scale = True        # forward(..., scale=m): the whole output times m as it joins the stream
 
@@ -106,8 +107,12 @@ class RoutedExperts(FeedForward):
         self.w_route = torch.cat(rows, dim=0).contiguous()           # the shared expert's gate rides behind the router's rows
         if self.has_correction:
             self.correction = tensors[self.names["correction"]].to(torch.float32).contiguous()
-        if self.gated:          # an expert's gate rows ahead of its up rows: one stream of [2F, D] per expert
-            self.w_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]])
+        if self.gated:
+            # One stream of [2F, D] per expert: gate and up rows by turns in blocks of 8 where the tensor-core products'
+            # gated epilogue can read them (silu, F a multiple of 8), else the gate rows ahead of the up rows.
+            self.up_block = linear.GATE_UP_BLOCK if self.activation == "silu" and self.F % linear.GATE_UP_BLOCK == 0 else 0
+            join = linear.interleave_gate_up if self.up_block else (lambda g, u: torch.cat([g, u]))
+            self.w_up = torch.stack([join(tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")])
                                      for e in range(self.E)]).contiguous()
         else:
             self.w_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.E)]).contiguous()
@@ -134,10 +139,11 @@ class RoutedExperts(FeedForward):
             # tile of the tcgen05 product reads one expert's weight; the second product reads the first one's rows as
             # they lie, and the combination finds each pair's row through the order's inverse.
             src, dst, tile_group = ops.group_rows_padded(ids.view(-1), self.E)
-            u = ops.gemm_tc_grouped(ops.gather_rows(h, src, self.top), self.w_up, tile_group, h.dtype)
-            if self.gated:
+            u = ops.gemm_tc_grouped(ops.gather_rows(h, src, self.top), self.w_up, tile_group, h.dtype,
+                                    swiglu=self.gated and self.up_block > 0)     # silu(gate) * up in the product's epilogue
+            if self.gated and not self.up_block:
                 u = ops.gated_act(u, None, self.activation, h.dtype)     # [rows, 2F] -> act(gate columns) * up columns
-            elif self.activation is not None:
+            elif not self.gated and self.activation is not None:
                 ops.activation(u, self.activation, out=u)
             y = ops.gemm_tc_grouped(u, self.w_down, tile_group, torch.float32)
             out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
@@ -151,14 +157,14 @@ class RoutedExperts(FeedForward):
             u = torch.empty((T * self.top, n_up), dtype=h.dtype, device=h.device)
             ops.grouped_gemm(h, self.w_up, u, listed=listed, a_div=self.top, act=None if self.gated else self.activation)
             if self.gated:
-                u = ops.gated_act(u, None, self.activation, h.dtype)
+                u = ops.swiglu(u, self.up_block) if self.up_block else ops.gated_act(u, None, self.activation, h.dtype)
             y = torch.empty((T * self.top, self.D), dtype=torch.float32, device=h.device)
             ops.grouped_gemm(u, self.w_down, y, listed=listed)
             out = residual if residual is not None else torch.empty((T, self.D), dtype=torch.float32, device=h.device)
             ops.moe_combine(y, weights, out, accumulate=residual is not None, shared=shared, shared_gate=gate,
                             shared_scale=scale, **more)
             return None if residual is not None else out
-        u = ops.moe_up(h, self.w_up, ids, self.activation, gated=self.gated)
+        u = ops.moe_up(h, self.w_up, ids, self.activation, gated=self.gated, block=self.up_block)
         more = dict(h=h if self.identity else None, shared_scale=scale)
         if residual is None:
             out = torch.empty((h.shape[0], self.D), dtype=torch.float32, device=h.device)

@@ -294,7 +294,7 @@ def test_random_weights_from_a_configuration_and_the_kernels_that_served_it():
     ran = ops.launches_since(before)
     assert [len(o) for o in out] == [5, 5]
     for kernel in ("embedding_pairs", "causal_conv", "rope_partial", "attn_prefill_tc", "attn_decode:teams", "add_scaled",
-                   "small_proj", "moe_route", "group_rows_padded", "gather_rows", "gemm_tc_grouped", "gated_act", "moe_combine",
+                   "small_proj", "moe_route", "group_rows_padded", "gather_rows", "gemm_tc_grouped", "moe_combine",
                    "moe_up", "moe_down"):
         assert ran.get(kernel, 0) >= 1, (kernel, ran)
     assert ran.get("attention_plain", 0) == 0, ran

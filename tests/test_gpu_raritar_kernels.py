@@ -341,11 +341,11 @@ def test_pair_embedding_remembers_each_sequences_last_token(dtype, buckets, a, b
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps,add", [(4, True), (2, True), (7, False), (1, True)])
-def test_causal_convolution_carries_its_last_rows_between_steps(dtype, taps, add):
+@pytest.mark.parametrize("D", [40, 42, 2056])       # whole 16-byte pieces of channels; not; more than a block of threads covers
+def test_causal_convolution_carries_its_last_rows_between_steps(dtype, taps, add, D):
     """Portions of 1, 2, 3 and more rows (shorter and longer than the taps) of three sequences against the convolution of
     each whole sequence; the state of a slot's earlier owner is not read at a sequence's start."""
     ops = _ops()
-    D = 40
     w = _rand((D, taps), torch.float32, 5, scale=0.5)
     lens = [11, 6, 17]
     hs = [_rand((n, D), dtype, 10 + i) for i, n in enumerate(lens)]
@@ -514,6 +514,11 @@ def test_streamed_gated_experts_pass_identity_inputs_on(dtype, T, D, F, E, ident
     ref = _experts_ref(h, w_up, w_down, ids, weights, E, shared, zs, 0.7)
     x0 = _rand((T, D), torch.float32, 49)
     u = ops.moe_up(h, w_up, ids, "silu", gated=True)
+    if F % 8 == 0:          # the same rows with gate and up by turns in blocks of 8: the same u
+        from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+        turns = torch.stack([interleave_gate_up(w[:F], w[F:]) for w in w_up])
+        real = (ids < E).cpu()
+        assert torch.equal(ops.moe_up(h, turns, ids, "silu", gated=True, block=8).cpu()[real], u.cpu()[real])
     for accumulate in (False, True):
         x = x0.clone()
         ops.moe_down(u, w_down, ids, weights, x, accumulate=accumulate, shared=shared, shared_gate=zs,
@@ -536,8 +541,11 @@ def test_grouped_gated_experts_leave_identity_pairs_out_of_the_products(T, D, F,
     assert ((place < 0) == (flat >= E)).all() and len(set(place[place >= 0].tolist())) == int((flat < E).sum())
     groups = tile_group.cpu()
     assert all(int(groups[int(p) // 128]) == int(e) for p, e in zip(place.tolist(), flat.tolist()) if p >= 0)
-    u = ops.gemm_tc_grouped(ops.gather_rows(h, src, top), w_up, tile_group, h.dtype)
-    y = ops.gemm_tc_grouped(ops.gated_act(u, None, "silu", h.dtype), w_down, tile_group, torch.float32)
+    from longbow_quarrel_b200.kernels.linear import interleave_gate_up
+    turns = torch.stack([interleave_gate_up(w[:F], w[F:]) for w in w_up])
+    u = ops.gemm_tc_grouped(ops.gather_rows(h, src, top), turns, tile_group, h.dtype, swiglu=True)     # silu(gate) * up in the epilogue
+    assert tuple(u.shape) == (src.numel(), F)
+    y = ops.gemm_tc_grouped(u, w_down, tile_group, torch.float32)
     torch.cuda.synchronize()
     assert ops.gemm_tc_status() == 0
     out = ops.moe_combine(y, weights, torch.empty((T, D), dtype=torch.float32, device=DEV), accumulate=False, shared=shared,
