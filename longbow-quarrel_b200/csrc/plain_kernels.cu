@@ -122,9 +122,10 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
 }
 
 // The same sums for rows whose channels come in whole 16-byte pieces: a thread makes 16 / sizeof(T) neighbouring channels,
-// every tap's piece one load, the taps added in the same order as above.
+// every tap's piece one load, the taps added in the same order as above.  wt: the weight by taps, [taps, D], so that a
+// thread's weights of one tap are neighbours too.
 template <typename T>
-__global__ void __launch_bounds__(256) causal_conv_vec_kernel(const T* __restrict__ h, T* __restrict__ out, const float* __restrict__ w,
+__global__ void __launch_bounds__(256) causal_conv_vec_kernel(const T* __restrict__ h, T* __restrict__ out, const float* __restrict__ wt,
                                                               const float* __restrict__ state, const int* __restrict__ tok_seq,
                                                               const int* __restrict__ slots, const int* __restrict__ cu_rows, int D,
                                                               int taps, int add_input) {
@@ -161,8 +162,15 @@ __global__ void __launch_bounds__(256) causal_conv_vec_kernel(const T* __restric
                 v[4 * c] = f.x; v[4 * c + 1] = f.y; v[4 * c + 2] = f.z; v[4 * c + 3] = f.w;
             }
         }
+        const float4* wp = reinterpret_cast<const float4*>(wt + (size_t)j * D + d);
 #pragma unroll
-        for (int c = 0; c < V; ++c) acc[c] = fmaf(w[(size_t)(d + c) * taps + j], v[c], acc[c]);
+        for (int c = 0; c < V / 4; ++c) {
+            const float4 f = wp[c];
+            acc[4 * c] = fmaf(f.x, v[4 * c], acc[4 * c]);
+            acc[4 * c + 1] = fmaf(f.y, v[4 * c + 1], acc[4 * c + 1]);
+            acc[4 * c + 2] = fmaf(f.z, v[4 * c + 2], acc[4 * c + 2]);
+            acc[4 * c + 3] = fmaf(f.w, v[4 * c + 3], acc[4 * c + 3]);
+        }
     }
     uint4 raw;
     T* e = reinterpret_cast<T*>(&raw);
@@ -186,19 +194,22 @@ __global__ void __launch_bounds__(256) conv_state_kernel(const T* __restrict__ h
         }
 }
 
-LQ_EXPORT int lq_causal_conv(const void* h, void* out, int dtype, const float* w, float* state, const int* tok_seq, const int* slots,
-                             const int* cu_rows, int T, int B, int D, int taps, int add_input, cudaStream_t stream) {
+// wt (or null): the same weight laid out [taps, D]; with it, rows whose channels come in whole 16-byte pieces take the
+// kernel that makes 16 bytes of channels a thread.
+LQ_EXPORT int lq_causal_conv_by_taps(const void* h, void* out, int dtype, const float* w, const float* wt, float* state,
+                                     const int* tok_seq, const int* slots, const int* cu_rows, int T, int B, int D, int taps,
+                                     int add_input, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (taps < 1 || (taps > 1 && !state)) return LQ_BAD_SIZE;
     const int ny = (D + 1023) / 1024;
     int rc;
     typedef __nv_bfloat16 bf;
-    const bool pieces = (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
+    const bool pieces = wt != nullptr && (((uintptr_t)h | (uintptr_t)out | (uintptr_t)state | (uintptr_t)wt) & 15) == 0;
     if (dtype == LQ_F32 && pieces && D % 4 == 0)
         rc = launch_pdl(causal_conv_vec_kernel<float>, dim3(T, (D / 4 + 255) / 256), dim3(256), 0, stream, (const float*)h, (float*)out,
-                        w, (const float*)state, tok_seq, slots, cu_rows, D, taps, add_input);
+                        wt, (const float*)state, tok_seq, slots, cu_rows, D, taps, add_input);
     else if (dtype == LQ_BF16 && pieces && D % 8 == 0)
-        rc = launch_pdl(causal_conv_vec_kernel<bf>, dim3(T, (D / 8 + 255) / 256), dim3(256), 0, stream, (const bf*)h, (bf*)out, w,
+        rc = launch_pdl(causal_conv_vec_kernel<bf>, dim3(T, (D / 8 + 255) / 256), dim3(256), 0, stream, (const bf*)h, (bf*)out, wt,
                         (const float*)state, tok_seq, slots, cu_rows, D, taps, add_input);
     else if (dtype == LQ_F32)
         rc = launch_pdl(causal_conv_kernel<float>, dim3(T, ny), dim3(256), 0, stream, (const float*)h, (float*)out, w, (const float*)state,
@@ -212,6 +223,11 @@ LQ_EXPORT int lq_causal_conv(const void* h, void* out, int dtype, const float* w
     if (dtype == LQ_F32)
         return launch_pdl(conv_state_kernel<float>, dim3(B, ny), dim3(256), 0, stream, (const float*)h, state, slots, cu_rows, D, taps);
     return launch_pdl(conv_state_kernel<bf>, dim3(B, ny), dim3(256), 0, stream, (const bf*)h, state, slots, cu_rows, D, taps);
+}
+
+LQ_EXPORT int lq_causal_conv(const void* h, void* out, int dtype, const float* w, float* state, const int* tok_seq, const int* slots,
+                             const int* cu_rows, int T, int B, int D, int taps, int add_input, cudaStream_t stream) {
+    return lq_causal_conv_by_taps(h, out, dtype, w, nullptr, state, tok_seq, slots, cu_rows, T, B, D, taps, add_input, stream);
 }
 
 // ------------------------------------------------------------------ x += m * y (a branch that joins the stream with a multiplier)
@@ -332,6 +348,105 @@ LQ_EXPORT int lq_rmsnorm(const float* x, const float* gain, const int* rows, voi
                    : launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (float*)out, D, eps);
     return vec ? launch_pdl(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps)
                : launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps);
+}
+
+// ------------------------------------------------------------------ a branch joins the stream with a multiplier, and the next norm
+// x += m * y for rows of a branch's output y [T, D] (float32), then h = x / rms(x) * gain in the activation dtype: what
+// add_scaled and rmsnorm do one after the other, with one pass over the stream.  Sums run in rmsnorm's order.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+add_scaled_norm_kernel(float* __restrict__ x, const float* __restrict__ y, float m, const float* __restrict__ gain,
+                       TO* __restrict__ out, int D, float eps) {
+    __shared__ float partial[8];
+    __shared__ float scale_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    float* xr = x + (size_t)r * D;
+    const float* yr = y + (size_t)r * D;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < D; i += 256) {
+        const float v = fmaf(m, yr[i], xr[i]);
+        xr[i] = v;
+        s = fmaf(v, v, s);
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        scale_s = 1.0f / sqrtf(t / (float)D + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+    for (int i = threadIdx.x; i < D; i += 256) out[(size_t)r * D + i] = from_f32<TO>(xr[i] * scale * gain[i]);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+add_scaled_norm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, float m, const float* __restrict__ gain,
+                           TO* __restrict__ out, int D, float eps) {
+    __shared__ float partial[8];
+    __shared__ float scale_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, n4 = D >> 2;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)r * D);
+    const float4* yr = reinterpret_cast<const float4*>(y + (size_t)r * D);
+    float4 v[RMS_VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        int c = threadIdx.x + i * 256;
+        if (c < n4) {
+            const float4 a = xr[c], b = yr[c];
+            v[i] = make_float4(fmaf(m, b.x, a.x), fmaf(m, b.y, a.y), fmaf(m, b.z, a.z), fmaf(m, b.w, a.w));
+            xr[c] = v[i];
+        } else {
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        s = fmaf(v[i].x, v[i].x, s); s = fmaf(v[i].y, v[i].y, s);
+        s = fmaf(v[i].z, v[i].z, s); s = fmaf(v[i].w, v[i].w, s);
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        scale_s = 1.0f / sqrtf(t / (float)D + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        int c = threadIdx.x + i * 256;
+        if (c >= n4) break;
+        float4 g = g4[c];
+        float o0 = v[i].x * scale * g.x, o1 = v[i].y * scale * g.y, o2 = v[i].z * scale * g.z, o3 = v[i].w * scale * g.w;
+        if (sizeof(TO) == 4) {
+            reinterpret_cast<float4*>(out + (size_t)r * D)[c] = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+            uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            reinterpret_cast<uint2*>(out + (size_t)r * D)[c] = packed;
+        }
+    }
+}
+
+LQ_EXPORT int lq_add_scaled_norm(float* x, const float* y, float m, const float* gain, void* out, int out_dtype, int n_rows, int D,
+                                 float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return LQ_OK;
+    if (out_dtype != LQ_F32 && out_dtype != LQ_BF16) return LQ_BAD_DTYPE;
+    const bool vec = D % 4 == 0 && D <= 256 * 4 * RMS_VEC && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)gain | (uintptr_t)out) & 15) == 0;
+    typedef __nv_bfloat16 bf;
+    if (out_dtype == LQ_F32)
+        return vec ? launch_pdl(add_scaled_norm_vec_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, y, m, gain, (float*)out, D, eps)
+                   : launch_pdl(add_scaled_norm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, y, m, gain, (float*)out, D, eps);
+    return vec ? launch_pdl(add_scaled_norm_vec_kernel<bf>, dim3(n_rows), dim3(256), 0, stream, x, y, m, gain, (bf*)out, D, eps)
+               : launch_pdl(add_scaled_norm_kernel<bf>, dim3(n_rows), dim3(256), 0, stream, x, y, m, gain, (bf*)out, D, eps);
 }
 
 // ------------------------------------------------------------------ norm of a branch, added to the stream

@@ -181,21 +181,24 @@ def embedding_pairs(table: torch.Tensor, pairs: torch.Tensor, buckets: int, mul_
 
 
 def causal_conv(h: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, tok_seq, slots, cu_rows, B: int,
-                add_input: bool = True) -> torch.Tensor:
+                add_input: bool = True, w_by_taps: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = (h[t] +) sum_j w[:, j] h[t - taps + 1 + j] over each sequence's own rows, per channel; w float32 [D, taps].
     state float32 [slots, taps - 1, D]: the rows ahead of a step's first row (zero at a sequence's start), moved on
-    by the step's rows afterwards."""
+    by the step's rows afterwards.  w_by_taps: the same weight as contiguous float32 [taps, D]; with it, rows whose
+    channels come in whole 16-byte pieces take the kernel that makes 16 bytes of channels a thread (the same sums)."""
     T, D = h.shape
     taps = w.shape[1]
     if w.dtype != torch.float32 or w.shape[0] != D or not w.is_contiguous():
         raise KernelError("causal_conv: the taps must be contiguous float32 [D, taps]")
+    if w_by_taps is not None and (w_by_taps.dtype != torch.float32 or tuple(w_by_taps.shape) != (taps, D) or not w_by_taps.is_contiguous()):
+        raise KernelError("causal_conv: the weight by taps must be contiguous float32 [taps, D]")
     if taps > 1 and (state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps - 1, D) or not state.is_contiguous()):
         raise KernelError(f"causal_conv: the state must be contiguous float32 [slots, {taps - 1}, {D}]")
     out = torch.empty_like(h)
-    fn = _fn("plain_kernels", "lq_causal_conv", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                 c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(_contig(h, "h")), _p(out), dtype_code(h), _p(w), _p(state), _p(tok_seq), _p(slots), _p(cu_rows), T, B, D, taps,
-              int(add_input), _stream()), "causal_conv", kernels=2 if taps > 1 else 1)
+    fn = _fn("plain_kernels", "lq_causal_conv_by_taps", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(h, "h")), _p(out), dtype_code(h), _p(w), _p(w_by_taps), _p(state), _p(tok_seq), _p(slots), _p(cu_rows), T, B,
+              D, taps, int(add_input), _stream()), "causal_conv", kernels=2 if taps > 1 else 1)
     return out
 
 
@@ -206,6 +209,21 @@ def add_scaled(x: torch.Tensor, y: torch.Tensor, m: float) -> torch.Tensor:
     fn = _fn("plain_kernels", "lq_add_scaled", [c_void_p, c_void_p, c_float, c_longlong, c_void_p])
     _check(fn(_p(x), _p(y), float(m), x.numel(), _stream()), "add_scaled")
     return x
+
+
+def add_scaled_norm(x: torch.Tensor, y: torch.Tensor, m: float, gain: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """x += m * y in place (float32 [T, D] both), and the rows of the RMS norm that reads x next, x / rms(x) * gain in
+    out_dtype: add_scaled and rmsnorm in one pass over the stream, with their sums in the same order."""
+    T, D = x.shape
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or x.shape != y.shape or not x.is_contiguous() or not y.is_contiguous():
+        raise KernelError("add_scaled_norm: contiguous float32 tensors of one shape")
+    if gain.dtype != torch.float32 or gain.numel() != D or not gain.is_contiguous():
+        raise KernelError("add_scaled_norm: the gain must be contiguous float32 [D]")
+    out = torch.empty((T, D), dtype=out_dtype, device=x.device)
+    fn = _fn("plain_kernels", "lq_add_scaled_norm", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                                     c_void_p])
+    _check(fn(_p(x), _p(y), float(m), _p(gain), _p(out), dtype_code(out_dtype), T, D, float(eps), _stream()), "add_scaled_norm")
+    return out
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dtype,

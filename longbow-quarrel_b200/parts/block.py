@@ -17,6 +17,7 @@ from __future__ import annotations
 
 from ..kernels import ops
 from .base import Part, Runtime, StepContext
+from .norm import RMSNorm
 from .registry import make_part, register_part
 from .spec import LayerSpec
 
@@ -84,16 +85,23 @@ class PreNormBlock(Part):
         return self.norm1.foldable(n_rows) if self.mixer.folds_norm else None
 
     def _forward_plain(self, x, ctx: StepContext, cache_view, writes_cache: bool, state):
-        """The layer with a filter ahead of its mixer or a multiplier on its branches: every norm a kernel of its own."""
+        """The layer with a filter ahead of its mixer or a multiplier on its branches: the norms are kernels of their own,
+        except that the mixer's branch joins the stream in the kernel that makes the second norm's rows."""
         h = self.norm1.forward(x)
         if self.conv1 is not None:
             h = self.conv1.forward(h, ctx, state)
+        h2 = None
         if self.scale == 1.0:
             self.mixer.forward(h, ctx, cache_view, x, writes_cache)
         else:
-            ops.add_scaled(x, self.mixer.forward(h, ctx, cache_view, None, writes_cache), self.scale)
+            branch = self.mixer.forward(h, ctx, cache_view, None, writes_cache)
+            gain = self.norm2.gain if self.has_ffn and isinstance(self.norm2, RMSNorm) else None
+            if gain is not None and gain.dtype == x.dtype == branch.dtype and x.is_contiguous() and branch.is_contiguous():
+                h2 = ops.add_scaled_norm(x, branch, self.scale, gain, self.norm2.eps, self.norm2.runtime.act_dtype)
+            else:
+                ops.add_scaled(x, branch, self.scale)
         if self.has_ffn:
-            h = self.norm2.forward(x)
+            h = h2 if h2 is not None else self.norm2.forward(x)
             if self.scale == 1.0:
                 self.ffn.forward(h, ctx, x)
             elif getattr(self.ffn, "takes_scale", False):

@@ -25,15 +25,17 @@ class CausalConv(Part):
             raise ValueError(f"causal_conv: {taps} taps")
         self.runtime, self.channels, self.taps, self.name, self.add_input = runtime, channels, int(taps), name, bool(add_input)
         self.w: torch.Tensor | None = None
+        self.w_by_taps: torch.Tensor | None = None       # [taps, channels]: the layout the kernel of 16-byte pieces reads
 
     def weights(self):
         return {self.name: WeightSpec((self.channels, self.taps))}
 
     def load(self, tensors):
         self.w = tensors[self.name].to(torch.float32).contiguous()
+        self.w_by_taps = self.w.t().contiguous()
 
     def state_need(self):
         return StateNeed((self.taps - 1, self.channels), torch.float32) if self.taps > 1 else None
 
     def forward(self, h: torch.Tensor, ctx: StepContext, state) -> torch.Tensor:
-        return ops.causal_conv(h, self.w, state, ctx.tok_seq, ctx.slots, ctx.cu_rows, ctx.B, self.add_input)
+        return ops.causal_conv(h, self.w, state, ctx.tok_seq, ctx.slots, ctx.cu_rows, ctx.B, self.add_input, w_by_taps=self.w_by_taps)

@@ -293,7 +293,7 @@ def test_random_weights_from_a_configuration_and_the_kernels_that_served_it():
     out = eng.generate([[t % 300 for t in range(1, 701)], [4]], max_new_tokens=5, sampling=SamplingParams(temperature=0.0), stop_ids=[])
     ran = ops.launches_since(before)
     assert [len(o) for o in out] == [5, 5]
-    for kernel in ("embedding_pairs", "causal_conv", "rope_partial", "attn_prefill_tc", "attn_decode:teams", "add_scaled",
+    for kernel in ("embedding_pairs", "causal_conv", "rope_partial", "attn_prefill_tc", "attn_decode:teams", "add_scaled_norm",
                    "small_proj", "moe_route", "group_rows_padded", "gather_rows", "gemm_tc_grouped", "moe_combine",
                    "moe_up", "moe_down"):
         assert ran.get(kernel, 0) >= 1, (kernel, ran)

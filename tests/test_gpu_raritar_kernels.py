@@ -341,8 +341,9 @@ def test_pair_embedding_remembers_each_sequences_last_token(dtype, buckets, a, b
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps,add", [(4, True), (2, True), (7, False), (1, True)])
-@pytest.mark.parametrize("D", [40, 42, 2056])       # whole 16-byte pieces of channels; not; more than a block of threads covers
-def test_causal_convolution_carries_its_last_rows_between_steps(dtype, taps, add, D):
+@pytest.mark.parametrize("D,by_taps", [(40, True), (40, False), (42, True), (2056, True)])   # 16-byte pieces of channels (with the
+# weight by taps) and one channel a thread; a width without whole pieces; more than a block of threads covers
+def test_causal_convolution_carries_its_last_rows_between_steps(dtype, taps, add, D, by_taps):
     """Portions of 1, 2, 3 and more rows (shorter and longer than the taps) of three sequences against the convolution of
     each whole sequence; the state of a slot's earlier owner is not read at a sequence's start."""
     ops = _ops()
@@ -360,7 +361,7 @@ def test_causal_convolution_carries_its_last_rows_between_steps(dtype, taps, add
             # The engine zeroes a slot's state when a sequence starts in it; here the kernel is given the positions.
             for i in live:
                 state[slots[i]] = 0
-        out = ops.causal_conv(h, w, state, tok_seq, sl, cu, len(live), add)
+        out = ops.causal_conv(h, w, state, tok_seq, sl, cu, len(live), add, w_by_taps=w.t().contiguous() if by_taps else None)
         at = 0
         for i in live:
             got[i].append(out[at:at + portions[i]])
@@ -559,3 +560,24 @@ def test_grouped_gated_experts_leave_identity_pairs_out_of_the_products(T, D, F,
     x0 = _rand((T, D), torch.float32, 59)
     out = ops.moe_combine(y, weights, x0.clone(), accumulate=True, shared=shared, shared_gate=zs, shared_scale=0.5, **more)
     _close_on_average(out, ref + x0.double().cpu(), 4e-3)
+
+
+# ------------------------------------------------------------------ a branch joins the stream, and the next norm, in one kernel
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,D", [(5, 64), (3, 100), (2, 42), (4, 2048), (1, 8192 + 4)])
+def test_scaled_add_and_norm_in_one_pass_equal_the_two_kernels(out_dtype, T, D):
+    """x += m y and the rows of the norm that follows: bit for bit what add_scaled and rmsnorm give one after the other
+    (widths by float4 pieces, not, and wider than the kernel's registers hold), and close to float64."""
+    ops = _ops()
+    x, y, gain = _rand((T, D), torch.float32, 60), _rand((T, D), torch.float32, 61), _rand((D,), torch.float32, 62) + 1.0
+    two = x.clone()
+    ops.add_scaled(two, y, 0.7)
+    rows_two = ops.rmsnorm(two, gain, 1e-5, out_dtype)
+    one = x.clone()
+    rows_one = ops.add_scaled_norm(one, y, 0.7, gain, 1e-5, out_dtype)
+    assert torch.equal(one, two) and torch.equal(rows_one, rows_two)
+    ref = x.double().cpu() + 0.7 * y.double().cpu()
+    _close(one, ref, 1e-6)
+    want = ref / torch.sqrt((ref * ref).mean(-1, keepdim=True) + 1e-5) * gain.double().cpu()
+    _close(rows_one, want, 3e-6 if out_dtype == torch.float32 else 1e-6, 0.0 if out_dtype == torch.float32 else BF16_ULP)
