@@ -361,7 +361,7 @@ def raritar_config(size: str, window: int) -> dict:
            "router": {"experts": experts - 2, "identity": 2, "top": top, "groups": {"count": 8, "keep": 3}}}
     layers = [{"type": "attention", "mixer": dict(att, **({"kv_from": 0} if i == 3 else {})), "mlp": moe} for i in range(4)]
     return {"architecture": "Raritar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
-            "canon": {"taps": 4}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "canon": {"taps": 4}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 71}},
             "layers": layers, "max_positions": 8192}
 
 

@@ -83,7 +83,7 @@ CONFIGS = {
         attn(8, 2, 64, 64, window=64, keep=64, rot=SCALED_B, scale=0.11, cap=30.0, mlp=MOE_W),
         attn(2, 1, 128, 128, window=100, keep=3, rot={"dims": 64, "base": 1e4}, cap=50.0, mlp=MOE_W),
         attn(4, 2, 64, 64, window=40, keep=70, rot=SCALED_B, scale=0.2, kv_from=0, mlp=MOE_W),
-    ], mult=0.5, taps=4, bigram=(1021, 1000003, 999983)),
+    ], mult=0.5, taps=4, bigram=(2039, 1000003, 999983)),
     # each mechanism behind as little else as the design allows
     "only_attention": model(48, 90, [attn(4, 2, 16, 16, window=20, keep=3, rot={"dims": 8, "base": 100.0, "scaling": {
         "factor": 2.0, "low": 1.0, "high": 2.0, "original": 32}}, scale=0.4, cap=10.0)]),
