@@ -101,6 +101,47 @@ CONFIGS = {
 }
 
 
+def random_config(rng) -> dict:
+    """A configuration drawn by `rng` (a random.Random): 2 to 6 layers, each with its own head counts, head sizes (also ones
+    that no tensor-core kernel takes), value size, window, kept positions, rotation, cap and scale, or on an earlier layer's
+    keys and values; routers with any mix of real and identity outputs, groups and choices; any taps, hashing and multiplier."""
+    width, vocab = rng.choice([64, 96, 128, 192, 320]), rng.choice([257, 500, 1000])
+    layers: list = []
+    for _ in range(rng.randint(2, 6)):
+        own = [j for j, layer in enumerate(layers) if "kv_from" not in layer["mixer"]]
+        if own and rng.random() < 0.35:
+            kv_from = rng.choice(own)
+            src = layers[kv_from]["mixer"]
+            kv, dim, vdim, rot = src["kv_heads"], src["dim"], src["vdim"], src.get("rot")
+            heads = kv * rng.choice([1, 2, 4])
+        else:
+            kv_from = None
+            heads = rng.choice([1, 2, 4, 6, 8])
+            kv = rng.choice([k for k in (1, 2, 3, 4, 8) if heads % k == 0])
+            dim = rng.choice([16, 32, 48, 64, 64, 80, 96, 128])
+            vdim = rng.choice([dim, dim, dim, dim // 2, dim + 16])
+            rotated = rng.choice([0, dim // 2 // 2 * 2, dim])
+            rot = None
+            if rotated:
+                rot = {"dims": rotated, "base": rng.choice([100.0, 10000.0, 5e5])}
+                if rng.random() < 0.6:
+                    rot["scaling"] = {"factor": rng.choice([2.0, 8.0, 32.0]), "low": 1.0, "high": rng.choice([2.0, 4.0]),
+                                      "original": rng.choice([16, 64, 1024])}
+        window = rng.choice([None, 8, 24, 44, 64, 100])
+        mlp = None
+        if rng.random() < 0.8:
+            groups, per = rng.choice([1, 2, 4]), rng.choice([1, 2, 3, 4])
+            identity = min(rng.choice([0, 0, 1, 2, 4]), groups * per - 1)
+            kept = rng.randint(1, groups)
+            mlp = moe(groups * per - identity, rng.randint(1, min(kept * per, 4)), rng.choice([16, 24, 40, 64]), identity=identity,
+                      groups=(groups, kept) if groups > 1 else None, shared=rng.choice([None, 32, 96]))
+        layers.append(attn(heads, kv, dim, vdim, window=window, keep=rng.choice([0, 1, 4, 9, 64]) if window else 0, rot=rot,
+                           scale=rng.choice([dim ** -0.5, 0.1, 0.2]), cap=rng.choice([None, 10.0, 30.0]), kv_from=kv_from, mlp=mlp))
+    return model(width, vocab, layers, eps=rng.choice([1e-5, 1e-6]), mult=rng.choice([None, 0.5, 0.7, 1.3]),
+                 taps=rng.choice([None, 2, 3, 4]),
+                 bigram=rng.choice([None, (rng.choice([97, 509, 4099]), rng.randint(1, 100), rng.randint(1, 100))]))
+
+
 def make_folder(tmp, name, seed: int = 0, std: float = 0.1, gain_std: float = 0.2, dtype=torch.bfloat16) -> Path:
     """A model folder with random weights, written by the framework's random-weights mode."""
     import longbow_quarrel_b200  # noqa: F401

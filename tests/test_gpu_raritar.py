@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_raritar
-from raritar_models import CONFIGS, bound, firm_rows, load, make_folder, row_errors, tokens
+from raritar_models import CONFIGS, bound, firm_rows, load, make_folder, random_config, row_errors, tokens
 from trace_tools import ROOT, Trace, run_trace, split, trace_batches, trace_chunked, trace_last_one_by_one, trace_mixed, trace_whole
 
 pytestmark = pytest.mark.gpu
@@ -153,6 +153,24 @@ def test_every_cut_of_every_request_matches_plain(tmp_path, name, dtype):
                     if r == rid:
                         err = float(row_errors(row, cuts["whole"][(r, pos)]))
                         assert err < 2 * tol, f"{what} against whole: {rid} position {pos}: {err:.3g}, bound {2 * tol:.3g}"
+
+
+@pytest.mark.parametrize("seed", [3, 12, 29])
+def test_configurations_drawn_at_random_match_plain(tmp_path, seed):
+    """Sizes and options that nobody chose: whole, the last 30 tokens one by one and an unequal batch, in both precisions."""
+    import random
+    rng = random.Random(seed)
+    folder = make_folder(tmp_path, random_config(rng), seed=seed, std=rng.choice([0.1, 0.2]))
+    cfg, _ = load(folder)
+    requests = {rid: tokens(n, cfg["vocab"], 50 * seed + i) for i, (rid, n) in enumerate({"a": 150, "b": 70, "c": 33}.items())}
+    tr = Trace()
+    tr.extend(trace_whole(requests), "whole:")
+    tr.extend(trace_last_one_by_one(requests, n_last=30), "tail:")
+    tr.extend(trace_batches(requests, {"a": 110, "b": 40, "c": 3}, width=3), "batched:")
+    for dtype in DTYPES:
+        got = run_trace(folder, dtype, tr, tmp_path / ("out_" + dtype))
+        for what in ("whole", "tail", "batched"):
+            _check(split(got, what + ":"), requests, folder, dtype, f"seed {seed} {dtype} {what}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
