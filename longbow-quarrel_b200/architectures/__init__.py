@@ -1,1 +1,1 @@
-from . import fetorax, llama, raritar, zoporax  # noqa: F401  (registers LlamaForCausalLM, Fetorax, Raritar and Zoporax)
+from . import fetorax, lavutar, llama, raritar, zoporax  # noqa: F401  (registers LlamaForCausalLM, Fetorax, Lavutar, Raritar and Zoporax)

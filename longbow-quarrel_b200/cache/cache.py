@@ -11,7 +11,7 @@ import numpy as np
 import torch
 
 from ..parts.base import CacheNeed
-from .group import CacheGroup, CacheSizing
+from .group import CacheGroup, CacheSizing, SeveralGroups
 from .paged import PagedKVGroup
 from .slots import CacheError, SlotAllocator
 from .state import StateGroup
@@ -48,13 +48,20 @@ class Cache:
             for e in g.entries:
                 self._views[e] = g.view(e)
 
+    def _flat_groups(self) -> list[CacheGroup]:
+        """Every group that holds storage, those inside a group of several included."""
+        out = []
+        for g in self.groups:
+            out += g.flat() if isinstance(g, SeveralGroups) else [g]
+        return out
+
     @property
     def kv_groups(self) -> list[PagedKVGroup]:
-        return [g for g in self.groups if isinstance(g, PagedKVGroup)]
+        return [g for g in self._flat_groups() if isinstance(g, PagedKVGroup)]
 
     @property
     def state_groups(self) -> list[StateGroup]:
-        return [g for g in self.groups if isinstance(g, StateGroup)]
+        return [g for g in self._flat_groups() if isinstance(g, StateGroup)]
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:

@@ -66,3 +66,56 @@ class CacheGroup:
 
     def pages_in_use(self) -> int:
         return 0
+
+
+class SeveralGroups(CacheGroup):
+    """The groups of a need that is several needs at once (`parts.base.SeveralNeeds`): every call goes to each of
+    them in turn, and an entry's view is the tuple of their views."""
+
+    def __init__(self, entries: list[int], groups: list):
+        """groups: one for each of the needs; None for a side that keeps nothing (its view is None)."""
+        self.entries, self.views_of = list(entries), list(groups)
+        self.groups = [g for g in groups if g is not None]
+
+    def start(self, slot: int) -> None:
+        for g in self.groups:
+            g.start(slot)
+
+    def reserve(self, slot: int, old_len: int, new_len: int) -> None:
+        for g in self.groups:
+            g.reserve(slot, old_len, new_len)
+
+    def commit(self, slot: int, length: int) -> None:
+        for g in self.groups:
+            g.commit(slot, length)
+
+    def reserve_one_each(self, slots, old_lens) -> None:
+        for g in self.groups:
+            g.reserve_one_each(slots, old_lens)
+
+    def commit_one_each(self, slots, new_lens) -> None:
+        for g in self.groups:
+            g.commit_one_each(slots, new_lens)
+
+    def release(self, slot: int) -> None:
+        for g in self.groups:
+            g.release(slot)
+
+    def upload(self) -> None:
+        for g in self.groups:
+            g.upload()
+
+    def view(self, entry: int):
+        return tuple(g.view(entry) if g is not None else None for g in self.views_of)
+
+    def nbytes(self) -> int:
+        return sum(g.nbytes() for g in self.groups)
+
+    def pages_in_use(self) -> int:
+        return sum(g.pages_in_use() for g in self.groups)
+
+    def flat(self) -> list[CacheGroup]:
+        out = []
+        for g in self.groups:
+            out += g.flat() if isinstance(g, SeveralGroups) else [g]
+        return out

@@ -7,7 +7,9 @@ Here every sequence of a batch has its own length, so storage is a pool of pages
 `page_size` tokens, [entry][page][kv_head][token][head_dim], and each slot has a row
 of page numbers.  A group whose layers attend to a window only gives pages back as
 they fall out of the window, so it holds a window's worth of pages per sequence; with
-`keep_first`, the pages that hold a sequence's first positions stay with it as well.
+`keep_first`, the pages that hold a sequence's first positions stay with it as well.  A group
+whose layers see only a position's own block of `chunk` positions gives back the pages that lie
+wholly below the block of the sequence's next position.
 """
 from __future__ import annotations
 
@@ -23,7 +25,10 @@ NO_PAGE = -1
 class PagedKVGroup(CacheGroup):
     def __init__(self, entries: list[int], n_kv_heads: int, head_dim: int, window: int | None, n_pages: int,
                  page_size: int, max_slots: int, max_pages_per_seq: int, dtype: torch.dtype, device,
-                 v_head_dim: int | None = None, values: bool = True, keep_first: int = 0):
+                 v_head_dim: int | None = None, values: bool = True, keep_first: int = 0, chunk: int | None = None):
+        if chunk is not None and window is not None:
+            raise CacheError("a group of cache entries has a window or blocks of positions, not both")
+        self.chunk = int(chunk) if chunk else None
         self.entries = list(entries)
         self.index = {e: i for i, e in enumerate(self.entries)}
         self.n_kv_heads, self.head_dim, self.window = n_kv_heads, head_dim, window
@@ -65,6 +70,8 @@ class PagedKVGroup(CacheGroup):
 
     def first_needed(self, length: int) -> int:
         """The lowest position a later token of a sequence of `length` tokens can attend to."""
+        if self.chunk is not None:
+            return (length // self.chunk) * self.chunk        # the block that holds the next position
         if self.window is None:
             return 0
         return max(0, length - self.window + 1)
@@ -92,7 +99,7 @@ class PagedKVGroup(CacheGroup):
 
     def trim(self, slot: int, length: int) -> None:
         """Give back the pages that lie wholly below the window of a sequence of `length` tokens."""
-        if self.window is None:
+        if self.window is None and self.chunk is None:
             return
         keep_from = self.first_needed(length) // self.page_size
         row = self.table[slot]
@@ -113,6 +120,12 @@ class PagedKVGroup(CacheGroup):
                 self.reserve(slot, old, old + 1)
 
     def commit_one_each(self, slots, new_lens) -> None:
+        if self.chunk is not None:
+            # Pages fall out only when the next position starts a block.
+            for slot, length in zip(slots.tolist(), new_lens.tolist()):
+                if length % self.chunk == 0:
+                    self.trim(slot, length)
+            return
         if self.window is None:
             return
         # A page falls out of the window only when the window's lower end reaches the next page.
@@ -174,4 +187,5 @@ class KVView:
         self.page_table = group.table_dev
         self.page_size = group.page_size
         self.window = group.window
+        self.chunk = group.chunk
         self.n_kv_heads, self.head_dim, self.v_head_dim = group.n_kv_heads, group.head_dim, group.v_head_dim

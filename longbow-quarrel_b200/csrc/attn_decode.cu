@@ -128,7 +128,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv
     // Positions, slots and page table are written before the step starts, never by a kernel of the
     // step, so they may be read before the kernel ahead is known to have finished.
     const int pos = tok_pos[tok], len = pos + 1;
-    const int start = (window > 0 && pos >= window) ? pos - window + 1 : 0;
+    const int start = lq_first_key(pos, window);
     const int* pt = page_table + (size_t)slots[tok_seq[tok]] * pt_stride;
 
     const int first_tile = start / TILE;

@@ -83,7 +83,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
     const int len = kv_len[seq];
     const int* pt = page_table + (size_t)slots[seq] * pt_stride;
     const int pos_last = pos0 + n_rows - 1;
-    const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
+    const int key_first = lq_first_key(pos0, window);
     // With kept first positions the block walks the tiles of the first `keep_first` keys that lie ahead of its
     // window (`kept` of them) and then the window's: step n stands for tile n when n < kept, else tile_lo - kept + n.
     const int tile_lo = key_first / BLOCK_N;
@@ -125,9 +125,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
     uint32_t qf[KD][4];
 
     const int prow0 = pos0 + warp * 16 + g, prow1 = prow0 + 8;          // positions of this thread's two rows
+    const int first0 = lq_first_key(prow0, window), first1 = lq_first_key(prow1, window);       // the first key each of them sees
     const bool row0ok = warp * 16 + g < n_rows, row1ok = warp * 16 + g + 8 < n_rows;
     const int warp_pos_hi = min(pos_last, pos0 + warp * 16 + 15);        // last position any row of the warp has
-    const int warp_key_lo = (window > 0) ? max(0, pos0 + warp * 16 - window + 1) : 0;
+    const int warp_key_lo = lq_first_key(pos0 + warp * 16, window);
 
     for (int n = 0; n < n_tiles; ++n) {
         const int stage = n & 1, tile = tile_at(n);
@@ -174,8 +175,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     int key = kb + j * 8 + 2 * t + i;
-                    bool ok0 = row0ok && key <= prow0 && (window <= 0 || key > prow0 - window || key < keep_first);
-                    bool ok1 = row1ok && key <= prow1 && (window <= 0 || key > prow1 - window || key < keep_first);
+                    bool ok0 = row0ok && key <= prow0 && (key >= first0 || key < keep_first);
+                    bool ok1 = row1ok && key <= prow1 && (key >= first1 || key < keep_first);
                     float a = s[j][i], b = s[j][2 + i];
                     if (cap_pre > 0.f) {          // capped scores: tanh(s scale / c); scale_log2 is then c log2(e)
                         a = tanh_fast(a * cap_pre);

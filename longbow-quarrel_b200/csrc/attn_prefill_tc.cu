@@ -137,7 +137,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int len = kv_len[seq];
     const int* pt = page_table + (size_t)slots[seq] * pt_stride;
     const int pos_last = pos0 + n_rows - 1;
-    const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
+    const int first_last = lq_first_key(pos_last, window);    // a tile from here on is inside every row's mask
+    const int key_first = lq_first_key(pos0, window);
     // With kept first positions the block walks the tiles of the first `keep_first` keys that lie ahead of its
     // window (`kept` of them) and then the window's: step j stands for tile j when j < kept, else tile_lo - kept + j.
     const int tile_lo = key_first / BN;
@@ -223,6 +224,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int pos_r = pos0 + r;
+        const int first_r = lq_first_key(pos_r, window);      // the first key this row sees
         const bool row_ok = r < n_rows;
         constexpr int NC = BN / PARTS;                    // keys of a tile of this thread
         constexpr int OC = HD / PARTS;                    // output columns of this thread
@@ -246,7 +248,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int c = 0; c < NC; ++c) t[c] = tanh_fast(t[c] * cap_pre);
             }
             // Tiles that lie wholly inside every row's range (most of them) need no mask.
-            const bool whole = n_rows == BM && tb + BN - 1 <= pos0 && tb + BN <= len && (window <= 0 || tb > pos_last - window);
+            const bool whole = n_rows == BM && tb + BN - 1 <= pos0 && tb + BN <= len && tb >= first_last;
             // Maxima of the raw scores (the scale is positive: it is applied to the maximum, and to the scores
             // inside the exponent's multiply-add).
             float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
@@ -257,7 +259,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     const int key = kb + c;
-                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window || key < keep_first);
+                    const bool vis = row_ok && key <= pos_r && key < len && (key >= first_r || key < keep_first);
                     t[c] = vis ? t[c] : -CUDART_INF_F;
                     mx[c & 3] = fmaxf(mx[c & 3], t[c]);
                 }
@@ -420,7 +422,8 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int len = kv_len[seq];
     const int* pt = page_table + (size_t)slots[seq] * pt_stride;
     const int pos_last = pos0 + n_rows - 1;
-    const int key_first = (window > 0 && pos0 >= window) ? pos0 - window + 1 : 0;
+    const int first_last = lq_first_key(pos_last, window);    // a tile from here on is inside every row's mask
+    const int key_first = lq_first_key(pos0, window);
     // With kept first positions the block walks the tiles of the first `keep_first` keys that lie ahead of its
     // window (`kept` of them) and then the window's: step j stands for tile j when j < kept, else tile_lo - kept + j.
     const int tile_lo = key_first / BN;
@@ -509,6 +512,7 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t tmem_s = tmem_base + chain * BN + lane_base;              // S, then P in its first 64 columns
         const uint32_t tmem_o = tmem_base + 2 * BN + chain * HD + lane_base;
         const int pos_r = pos0 + r;
+        const int first_r = lq_first_key(pos_r, window);      // the first key this row sees
         const bool row_ok = r < n_rows;
         float m_ref = -CUDART_INF_F, l = 0.f;
         bool ok = true;
@@ -525,7 +529,7 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
                 for (int c = 0; c < BN; ++c) t[c] = tanh_fast(t[c] * cap_pre);
             }
-            const bool whole = n_rows == BM && kb + BN - 1 <= pos0 && kb + BN <= len && (window <= 0 || kb > pos_last - window);
+            const bool whole = n_rows == BM && kb + BN - 1 <= pos0 && kb + BN <= len && kb >= first_last;
             float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (whole) {
 #pragma unroll
@@ -534,7 +538,7 @@ attn_prefill_two_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int key = kb + c;
-                    const bool vis = row_ok && key <= pos_r && key < len && (window <= 0 || key > pos_r - window || key < keep_first);
+                    const bool vis = row_ok && key <= pos_r && key < len && (key >= first_r || key < keep_first);
                     t[c] = vis ? t[c] : -CUDART_INF_F;
                     mx[c & 3] = fmaxf(mx[c & 3], t[c]);
                 }

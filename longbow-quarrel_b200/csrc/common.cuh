@@ -27,6 +27,13 @@ static inline int lq_launch_status() {
     return e == cudaSuccess ? LQ_OK : (int)e;
 }
 
+// The first key that a row at position p sees under a mask given as one integer: w > 0, a sliding window of the
+// last w positions; w < 0, the row's own block of -w positions (blocks are counted from the sequence's first
+// position); 0, every earlier position.  It never decreases as p grows.
+__device__ __forceinline__ int lq_first_key(int p, int w) {
+    return w > 0 ? max(0, p - w + 1) : (w < 0 ? p - p % (-w) : 0);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -350,6 +350,103 @@ LQ_EXPORT int lq_rmsnorm(const float* x, const float* gain, const int* rows, voi
                : launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, gain, rows, (__nv_bfloat16*)out, D, eps);
 }
 
+// ------------------------------------------------------------------ layer norm
+// out = (x - mean) / sqrt(var + eps) * gain + bias over rows of the 32-bit stream, var the mean of the squared
+// deviations from the mean (two passes: the mean first, then the deviations), all in float32.  Optionally the
+// rows first take up to two branches, x += m1 * y1 + m2 * y2 (in place; a mixer of two sides joining the stream),
+// so that the addition and the norm that reads the stream next are one pass.  rows (optional) picks rows (then
+// nothing is added).  A block per row; sums run in an order that depends on D alone.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(float* __restrict__ x, const float* __restrict__ y1, float m1, const float* __restrict__ y2, float m2,
+                 const float* __restrict__ gain, const float* __restrict__ bias, const int* __restrict__ rows,
+                 TO* __restrict__ out, int D, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float partial[8];
+    __shared__ float stat;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const size_t at = (size_t)(rows ? rows[r] : r) * D;
+    float* xr = x + at;
+    float s = 0.f;
+    for (int i = tid; i < D; i += 256) {
+        float v = xr[i];
+        if (y1) {
+            v = fmaf(m1, y1[at + i], v);
+            if (y2) v = fmaf(m2, y2[at + i], v);
+            xr[i] = v;
+        }
+        s += v;
+    }
+    s = warp_sum(s);
+    if ((tid & 31) == 0) partial[tid >> 5] = s;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        stat = t / (float)D;
+    }
+    __syncthreads();
+    const float mean = stat;
+    float q = 0.f;
+    for (int i = tid; i < D; i += 256) {
+        const float d = xr[i] - mean;
+        q = fmaf(d, d, q);
+    }
+    q = warp_sum(q);
+    __syncthreads();
+    if ((tid & 31) == 0) partial[tid >> 5] = q;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        stat = 1.0f / sqrtf(t / (float)D + eps);
+    }
+    __syncthreads();
+    const float inv = stat;
+    for (int i = tid; i < D; i += 256)
+        out[(size_t)r * D + i] = from_f32<TO>((xr[i] - mean) * inv * gain[i] + (bias ? bias[i] : 0.f));
+}
+
+LQ_EXPORT int lq_layernorm(float* x, const float* y1, float m1, const float* y2, float m2, const float* gain, const float* bias,
+                           const int* rows, void* out, int out_dtype, int n_rows, int D, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return LQ_OK;
+    if ((rows && y1) || (y2 && !y1)) return LQ_BAD_SIZE;
+    if (out_dtype == LQ_F32)
+        return launch_pdl(layernorm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, y1, m1, y2, m2, gain, bias, rows,
+                          (float*)out, D, eps);
+    if (out_dtype == LQ_BF16)
+        return launch_pdl(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, y1, m1, y2, m2, gain, bias, rows,
+                          (__nv_bfloat16*)out, D, eps);
+    return LQ_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------ two streams side by side, as a product's input
+// out[t] = [a[t], b[t]] in the activation dtype from two float32 [T, D] (the stream and the embedding's rows ahead of
+// the product that mixes them at the start of a pass over repeated layers).
+template <typename TO>
+__global__ void side_by_side_kernel(const float* __restrict__ a, const float* __restrict__ b, TO* __restrict__ out, int D,
+                                    size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / (2 * D);
+    const int c = (int)(i % (2 * D));
+    out[i] = from_f32<TO>(c < D ? a[t * D + c] : b[t * D + c - D]);
+}
+
+LQ_EXPORT int lq_side_by_side(const float* a, const float* b, void* out, int out_dtype, int T, int D, cudaStream_t stream) {
+    const size_t total = (size_t)T * 2 * D;
+    if (total == 0) return LQ_OK;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == LQ_F32)
+        return launch_pdl(side_by_side_kernel<float>, dim3(blocks), dim3(256), 0, stream, a, b, (float*)out, D, total);
+    if (out_dtype == LQ_BF16)
+        return launch_pdl(side_by_side_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, a, b, (__nv_bfloat16*)out, D, total);
+    return LQ_BAD_DTYPE;
+}
+
 // ------------------------------------------------------------------ a branch joins the stream with a multiplier, and the next norm
 // x += m * y for rows of a branch's output y [T, D] (float32), then h = x / rms(x) * gain in the activation dtype: what
 // add_scaled and rmsnorm do one after the other, with one pass over the stream.  Sums run in rmsnorm's order.
@@ -747,17 +844,62 @@ LQ_EXPORT int lq_rope_kv_write(void* qkv, int dtype, const float* cos_t, const f
 // into v_pages [..][vd] (with v_unit: each value head first divided by its root mean square, sqrt(mean(v^2) + v_eps)).
 // The rows may be float32 while queries and cache are bfloat16: a product's 32-bit sums
 // then meet their biases and angles before anything is rounded.
+// unit_norm (after the bias, ahead of the rotation; 32-bit, eps inside the root): 1, each of the n_rot heads is divided by
+// its own root mean square; 2, the queries (heads below k_first) are divided by the root mean square of all of them
+// together and the keys likewise, and each dimension is multiplied by norm_w[column] (the queries' weights, then the keys').
+// q_temp_every > 0: the queries are then multiplied by 1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1) at position p.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 rope_partial_kernel(const TI* buf, int stride, TO* qout, int qout_stride, const float* __restrict__ bias,
                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
                     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
                     const int* __restrict__ page_table, int pt_stride, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
-                    int n_rot, int k_first, int Hkv, int hd, int vd, int v_off, int page_size, int v_unit, float v_eps) {
+                    int n_rot, int k_first, int Hkv, int hd, int vd, int v_off, int page_size, int v_unit, float v_eps,
+                    int unit_norm, const float* __restrict__ norm_w, float norm_eps, float q_temp_coef, int q_temp_every) {
     pdl_launch_dependents();
     pdl_wait();
+    extern __shared__ float head_mul[];             // [n_rot] what each head is multiplied by (unit norm, query temperature)
     const int t = blockIdx.x, pos = tok_pos[t], half = rot >> 1;
     const TI* row = buf + (size_t)t * stride;
+    const bool scaled = unit_norm || q_temp_every > 0;
+    if (scaled) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (unit_norm) {
+            // Sums of squares, a warp per head, in an order that depends on hd alone.
+            for (int head = warp; head < n_rot; head += 8) {
+                const TI* p = row + (size_t)head * hd;
+                float ss = 0.f;
+                for (int j = lane; j < hd; j += 32) {
+                    const float v = to_f32(p[j]) + (bias ? bias[(size_t)head * hd + j] : 0.f);
+                    ss = fmaf(v, v, ss);
+                }
+                ss = warp_sum(ss);
+                if (lane == 0) head_mul[head] = ss;
+            }
+            __syncthreads();
+            if (unit_norm == 2) {
+                // One norm over all queries and one over all keys: the heads' sums added in the order of the heads.
+                float sq = 0.f, sk = 0.f;
+                for (int head = 0; head < k_first; ++head) sq += head_mul[head];
+                for (int head = k_first; head < n_rot; ++head) sk += head_mul[head];
+                __syncthreads();
+                const float iq = 1.f / sqrtf(sq / (float)(k_first * hd) + norm_eps);
+                const float ik = n_rot > k_first ? 1.f / sqrtf(sk / (float)((n_rot - k_first) * hd) + norm_eps) : 0.f;
+                for (int head = threadIdx.x; head < n_rot; head += 256) head_mul[head] = head < k_first ? iq : ik;
+            } else {
+                for (int head = threadIdx.x; head < n_rot; head += 256)
+                    head_mul[head] = 1.f / sqrtf(head_mul[head] / (float)hd + norm_eps);
+            }
+        } else {
+            for (int head = threadIdx.x; head < n_rot; head += 256) head_mul[head] = 1.f;
+        }
+        __syncthreads();
+        if (q_temp_every > 0) {
+            const float qt = 1.f + q_temp_coef * logf((float)((pos + 1) / q_temp_every) + 1.f);
+            for (int head = threadIdx.x; head < k_first; head += 256) head_mul[head] *= qt;
+            __syncthreads();
+        }
+    }
     TO* qrow = qout + (size_t)t * qout_stride;
     const float* cs = rot ? cos_t + (size_t)pos * half : nullptr;
     const float* sn = rot ? sin_t + (size_t)pos * half : nullptr;
@@ -773,15 +915,24 @@ rope_partial_kernel(const TI* buf, int stride, TO* qout, int qout_stride, const 
         const float* b = bias ? bias + (size_t)head * hd : nullptr;
         TO* qd = head < k_first ? qrow + (size_t)head * hd : nullptr;
         TO* kd = (k_pages && head >= k_first) ? k_pages + (at + (size_t)(head - k_first) * page_size) * hd : nullptr;
+        const float mul = scaled ? head_mul[head] : 1.f;
+        const float* nw = (unit_norm == 2 && norm_w) ? norm_w + (size_t)head * hd : nullptr;
         if (j < half) {
-            const float u = to_f32(p[j]) + (b ? b[j] : 0.f), w = to_f32(p[j + half]) + (b ? b[j + half] : 0.f);
+            float u = to_f32(p[j]) + (b ? b[j] : 0.f), w = to_f32(p[j + half]) + (b ? b[j + half] : 0.f);
+            if (scaled) {
+                u *= mul;
+                w *= mul;
+                if (nw) { u *= nw[j]; w *= nw[j + half]; }
+            }
             const float c = cs[j], s = sn[j];
             const TO o0 = from_f32<TO>(u * c - w * s), o1 = from_f32<TO>(w * c + u * s);
             if (qd) { qd[j] = o0; qd[j + half] = o1; }
             if (kd) { kd[j] = o0; kd[j + half] = o1; }
         } else {
             const int d = j + half;
-            const TO o = from_f32<TO>(to_f32(p[d]) + (b ? b[d] : 0.f));
+            float v = to_f32(p[d]) + (b ? b[d] : 0.f);
+            if (scaled) v = nw ? v * mul * nw[d] : v * mul;
+            const TO o = from_f32<TO>(v);
             if (qd) qd[d] = o;
             if (kd) kd[d] = o;
         }
@@ -818,13 +969,17 @@ LQ_EXPORT int lq_rope_partial(const void* buf, int in_dtype, int stride, void* q
                               const float* bias, const float* cos_t, const float* sin_t, int rot, const int* tok_pos,
                               const int* tok_seq, const int* slots, const int* page_table, int pt_stride, void* k_pages,
                               void* v_pages, int T, int n_rot, int k_first, int Hkv, int hd, int vd, int v_off,
-                              int page_size, int v_unit, float v_eps, cudaStream_t stream) {
+                              int page_size, int v_unit, float v_eps, int unit_norm, const float* norm_w, float norm_eps,
+                              float q_temp_coef, int q_temp_every, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (rot % 2 || rot > hd || (rot && (!cos_t || !sin_t)) || (!k_pages) != (!v_pages)) return LQ_BAD_SIZE;
+    if (unit_norm < 0 || unit_norm > 2 || n_rot > 8192) return LQ_BAD_SIZE;
+    const size_t smem = (size_t)n_rot * sizeof(float);
     typedef __nv_bfloat16 bf;
-#define LQ_GO(TI, TO) return launch_pdl(rope_partial_kernel<TI, TO>, dim3(T), dim3(256), 0, stream, (const TI*)buf, stride, \
+#define LQ_GO(TI, TO) return launch_pdl(rope_partial_kernel<TI, TO>, dim3(T), dim3(256), smem, stream, (const TI*)buf, stride, \
         (TO*)qout, qout_stride, bias, cos_t, sin_t, rot, tok_pos, tok_seq, slots, page_table, pt_stride, (TO*)k_pages, \
-        (TO*)v_pages, n_rot, k_first, Hkv, hd, vd, v_off, page_size, v_unit, v_eps)
+        (TO*)v_pages, n_rot, k_first, Hkv, hd, vd, v_off, page_size, v_unit, v_eps, unit_norm, norm_w, norm_eps, q_temp_coef, \
+        q_temp_every)
     if (in_dtype == LQ_F32 && out_dtype == LQ_F32) LQ_GO(float, float);
     if (in_dtype == LQ_BF16 && out_dtype == LQ_BF16) LQ_GO(bf, bf);
     if (in_dtype == LQ_F32 && out_dtype == LQ_BF16) LQ_GO(float, bf);
@@ -933,31 +1088,33 @@ LQ_EXPORT int lq_add_bias(float* x, const float* bias, int T, int D, cudaStream_
     return launch_pdl(add_bias_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, bias, total, D);
 }
 
-// x[r, c] *= sigmoid(gate[r, c]) (act 1) or silu(gate[r, c]) (act 2), in place; gate rows may be strided.
+// x[r, c] *= sigmoid(gate[r, c / group]) (act 1) or silu(...) (act 2), in place; gate rows may be strided.  group 1: a gate
+// for every value; group n: one gate for n neighbouring columns (a head's values behind one number).
 template <typename T, typename TG>
-__global__ void gate_mul_kernel(T* __restrict__ x, const TG* __restrict__ gate, int gate_stride, int cols, size_t total, int act) {
+__global__ void gate_mul_kernel(T* __restrict__ x, const TG* __restrict__ gate, int gate_stride, int cols, size_t total, int act,
+                                int group) {
     pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const float g = to_f32(gate[(i / cols) * gate_stride + i % cols]);
+    const float g = to_f32(gate[(i / cols) * gate_stride + (i % cols) / group]);
     const float sg = 1.f / (1.f + expf(-g));
     x[i] = from_f32<T>(to_f32(x[i]) * (act == 1 ? sg : g * sg));
 }
 
 LQ_EXPORT int lq_gate_mul(void* x, const void* gate, int gate_stride, int dtype, int gate_dtype, int rows, int cols, int act,
-                          cudaStream_t stream) {
+                          int group, cudaStream_t stream) {
     const size_t total = (size_t)rows * cols;
     if (total == 0) return LQ_OK;
-    if (act != 1 && act != 2) return LQ_BAD_SIZE;
+    if ((act != 1 && act != 2) || group < 1 || cols % group) return LQ_BAD_SIZE;
     unsigned blocks = (unsigned)((total + 255) / 256);
     typedef __nv_bfloat16 bf;
     if (dtype == LQ_F32 && gate_dtype == LQ_F32)
-        return launch_pdl(gate_mul_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride, cols, total, act);
+        return launch_pdl(gate_mul_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)gate, gate_stride, cols, total, act, group);
     if (dtype == LQ_BF16 && gate_dtype == LQ_BF16)
-        return launch_pdl(gate_mul_kernel<bf, bf>, dim3(blocks), dim3(256), 0, stream, (bf*)x, (const bf*)gate, gate_stride, cols, total, act);
+        return launch_pdl(gate_mul_kernel<bf, bf>, dim3(blocks), dim3(256), 0, stream, (bf*)x, (const bf*)gate, gate_stride, cols, total, act, group);
     if (dtype == LQ_BF16 && gate_dtype == LQ_F32)
-        return launch_pdl(gate_mul_kernel<bf, float>, dim3(blocks), dim3(256), 0, stream, (bf*)x, (const float*)gate, gate_stride, cols, total, act);
+        return launch_pdl(gate_mul_kernel<bf, float>, dim3(blocks), dim3(256), 0, stream, (bf*)x, (const float*)gate, gate_stride, cols, total, act, group);
     return LQ_BAD_DTYPE;
 }
 
@@ -990,7 +1147,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
                        const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ slots, T* __restrict__ out, int H, int Hkv, int hd,
                        int page_size, float scale, int window, int vd, const float* __restrict__ sink,
-                       const TG* __restrict__ gate, int gate_stride, float cap, int keep_first) {
+                       const TG* __restrict__ gate, int gate_stride, float cap, int keep_first, int gate_per_head) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float sm[];
@@ -1001,7 +1158,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
     int pos = tok_pos[t];
     int slot = slots[tok_seq[t]];
     int kvh = h / (H / Hkv);
-    int start = (window > 0 && pos >= window) ? pos - window + 1 : 0;
+    int start = lq_first_key(pos, window);
     const T* qrow = q + (size_t)t * q_stride + (size_t)h * hd;
     for (int i = tid; i < hd; i += ATT_CHUNK) qs[i] = to_f32(qrow[i]);
     __syncthreads();
@@ -1057,10 +1214,17 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, const T* __restric
     }
     float o0 = acc0 / l, o1 = acc1 / l;
     if (gate) {
-        // The output gate: each value times sigmoid of the gate's value at the same place.
-        const TG* g = gate + (size_t)t * gate_stride + (size_t)h * vd;
-        if (tid < vd) o0 *= 1.f / (1.f + expf(-to_f32(g[tid])));
-        if (tid + ATT_CHUNK < vd) o1 *= 1.f / (1.f + expf(-to_f32(g[tid + ATT_CHUNK])));
+        // The output gate: each value times sigmoid of the gate's value at the same place, or (gate_per_head) every
+        // value of the head times sigmoid of the head's one number, gate [T, H].
+        if (gate_per_head) {
+            const float sg = 1.f / (1.f + expf(-to_f32(gate[(size_t)t * gate_stride + h])));
+            o0 *= sg;
+            o1 *= sg;
+        } else {
+            const TG* g = gate + (size_t)t * gate_stride + (size_t)h * vd;
+            if (tid < vd) o0 *= 1.f / (1.f + expf(-to_f32(g[tid])));
+            if (tid + ATT_CHUNK < vd) o1 *= 1.f / (1.f + expf(-to_f32(g[tid + ATT_CHUNK])));
+        }
     }
     T* orow = out + ((size_t)t * H + h) * vd;
     if (tid < vd) orow[tid] = from_f32<T>(o0);
@@ -1071,7 +1235,7 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
                                  const int* page_table, int pt_stride, const int* tok_pos, const int* tok_seq,
                                  const int* slots, void* out, int T, int H, int Hkv, int hd, int page_size,
                                  float scale, int window, int vd, const float* sink, const void* gate, int gate_stride,
-                                 int gate_dtype, float cap, int keep_first, cudaStream_t stream) {
+                                 int gate_dtype, float cap, int keep_first, int gate_per_head, cudaStream_t stream) {
     if (T <= 0) return LQ_OK;
     if (vd <= 0) vd = hd;
     if (vd > 2 * ATT_CHUNK || H % Hkv) return LQ_BAD_SIZE;
@@ -1080,15 +1244,15 @@ LQ_EXPORT int lq_attention_plain(const void* q, int q_stride, int dtype, const v
     if (dtype == LQ_F32)
         return launch_pdl(attention_plain_kernel<float, float>, grid, dim3(ATT_CHUNK), smem, stream, (const float*)q, q_stride, (const float*)k_pages,
             (const float*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots, (float*)out, H, Hkv, hd, page_size, scale, window,
-            vd, sink, (const float*)gate, gate_stride, cap, keep_first);
+            vd, sink, (const float*)gate, gate_stride, cap, keep_first, gate_per_head);
     else if (dtype == LQ_BF16 && gate && gate_dtype == LQ_F32)
         return launch_pdl(attention_plain_kernel<__nv_bfloat16, float>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const float*)gate, gate_stride, cap, keep_first);
+            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const float*)gate, gate_stride, cap, keep_first, gate_per_head);
     else if (dtype == LQ_BF16)
         return launch_pdl(attention_plain_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(ATT_CHUNK), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, page_table, pt_stride, tok_pos, tok_seq, slots,
-            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const __nv_bfloat16*)gate, gate_stride, cap, keep_first);
+            (__nv_bfloat16*)out, H, Hkv, hd, page_size, scale, window, vd, sink, (const __nv_bfloat16*)gate, gate_stride, cap, keep_first, gate_per_head);
     else
         return LQ_BAD_DTYPE;
     return lq_launch_status();

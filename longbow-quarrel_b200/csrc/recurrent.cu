@@ -2,8 +2,9 @@
 //
 //   S_t = a_t S_(t-1) + b_t k_t v_t^T          o_t = S_t^T q_t
 //
-// with a_t, b_t scalars per head and token.  Two instances:
+// with a_t, b_t scalars per head and token (or a_t a vector over the key channels: S_t = diag(a_t) S_(t-1) + ...).  Instances:
 //   retention   a_t = the head's fixed decay, b_t = 1
+//   channel decays   a_t[r] = sigmoid(z_t[r] + bias[r])^(1/tau) for key channel r, z from a 32-bit product of its own, b_t = 1
 //   mlstm       a_t = exp(f_t + m_(t-1) - m_t), b_t = exp(i_t - m_t), m_t = max(f_t + m_(t-1), i_t), m_0 = 0,
 //               i_t = cap tanh(x_i / cap), f_t = logsigmoid(cap tanh(x_f / cap)); the normaliser n_t (the same
 //               recurrence with v = 1) rides along as one more value column, so n_t . q_t is that column's output
@@ -43,6 +44,10 @@ struct ScanArgs {
     float* exp_neg_m;            // mlstm: [rows, H] exp(-m_t)
     int H, dk, dv;
     int in_act;                  // 0: q, k and v enter as stored; 1: each goes through silu first (in float32)
+    const float* decay_pre;      // channel decays: [rows, decay_stride], head h's dk pre-activations at column h * dk
+    int decay_stride;
+    const float* decay_bias;     // channel decays: [H * dk] or null
+    float inv_tau;               // channel decays: a = exp(logsigmoid(pre + bias) * inv_tau)
 };
 
 __device__ __forceinline__ float scan_in(float x, int act) { return act ? x / (1.f + expf(-x)) : x; }
@@ -54,7 +59,7 @@ __device__ __forceinline__ float scan_in(float x, int act) { return act ? x / (1
 // token by token (its only dependence); the outputs' partial sums stay in registers and are added across the
 // warp once per chunk, in a fixed order.  The block's tile of the state comes and goes through shared memory in
 // whole rows.
-template <typename T, int KR, bool MLSTM>
+template <typename T, int KR, bool MLSTM, bool VEC>
 __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
     pdl_launch_dependents();
     extern __shared__ float sm[];
@@ -68,6 +73,8 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
     float* gi = as2 + 2 * SC_CHUNK;              // [CHUNK] b_t of the chunk being staged
     float* ms = gi + SC_CHUNK;                   // [CHUNK + 1] the running maximum after the chunk being staged
     float* tile = ms + SC_CHUNK + 1;             // [dkx][COLS + 1]: the block's columns of the state
+    float* dsm = tile + (dk + 1) * (SC_COLS + 1);                 // channel decays: two buffers of [CHUNK][dk]
+    auto ds = [&](int buf) { return dsm + buf * qk_floats; };
     const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * SC_COLS;
     const int tid = threadIdx.x, c = tid / SC_R, rr = tid % SC_R, col = col0 + c;
     const int n_cols = min(SC_COLS, dvx - col0);
@@ -78,15 +85,16 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
     pdl_wait();
     const int row0 = a.cu_rows[b], row1 = a.cu_rows[b + 1];
     float m = 0.f;
-    float q_pf[KR], k_pf[KR], cs_pf[RF], sn_pf[RF], v_pf = 0.f, gi_pf = 0.f, gf_pf = 0.f;
+    float q_pf[KR], k_pf[KR], d_pf[VEC ? KR : 1], cs_pf[RF], sn_pf[RF], v_pf = 0.f, gi_pf = 0.f, gf_pf = 0.f;
     // Element e of a chunk's q (k) is token e / dk, dimension e % dk; thread tid holds e = tid + i * THREADS.
     // Which token and which place that is does not change from chunk to chunk: worked out once.
-    int e_tok[KR], e_off[KR], r_tok[RF], r_dim[RF];
+    int e_tok[KR], e_off[KR], e_dec[VEC ? KR : 1], r_tok[RF], r_dim[RF];
 #pragma unroll
     for (int i = 0; i < KR; ++i) {
         const int e = tid + i * SC_THREADS;
         e_tok[i] = e / dk;                                            // >= CHUNK beyond the chunk
         e_off[i] = e_tok[i] * a.stride + h * dk + e % dk;
+        if (VEC) e_dec[i] = e_tok[i] * a.decay_stride + h * dk + e % dk;
     }
 #pragma unroll
     for (int i = 0; i < RF; ++i) {
@@ -105,6 +113,7 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
             if (e_tok[i] < n) {
                 q_pf[i] = scan_in(to_f32(rows[e_off[i] + a.q_off]), a.in_act);
                 k_pf[i] = scan_in(to_f32(rows[e_off[i] + a.k_off]), a.in_act);
+                if (VEC) d_pf[i] = a.decay_pre[(size_t)t0 * a.decay_stride + e_dec[i]];
             }
         }
         if (half) {
@@ -140,6 +149,12 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
             if (e_tok[i] < n) {
                 qs(buf)[tid + i * SC_THREADS] = q_pf[i];
                 ks(buf)[tid + i * SC_THREADS] = k_pf[i];
+                if (VEC) {
+                    // The decay of this token's key channel: sigmoid(z + bias)^(1/tau), through the logarithm, in 32-bit.
+                    const int ch = h * dk + (tid + i * SC_THREADS) % dk;
+                    const float z = d_pf[i] + (a.decay_bias ? a.decay_bias[ch] : 0.f);
+                    ds(buf)[tid + i * SC_THREADS] = expf(log_sigmoid(z) * a.inv_tau);
+                }
             }
         }
         if (MLSTM && tid < 32) {
@@ -217,7 +232,7 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
         S[i] = r < dk ? tile[r * (SC_COLS + 1) + c] : 0.f;
     }
     if (MLSTM) m = tile[dk * (SC_COLS + 1)];
-    const float decay = MLSTM ? 0.f : a.decay[h];
+    const float decay = (MLSTM || VEC) ? 0.f : a.decay[h];
 
     if (row0 < row1) stage(row0, 0);
     int buf = 0;
@@ -234,11 +249,12 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
                 const float bv = vs(buf)[t * SC_COLS + c];
                 const float* kt = ks(buf) + t * dk;
                 const float* qt = qs(buf) + t * dk;
+                const float* dt = VEC ? ds(buf) + t * dk : nullptr;
 #pragma unroll
                 for (int i = 0; i < KR; ++i) {
                     const int r = i * SC_R + rr;
                     if (r < dk) {
-                        S[i] = fmaf(at, S[i], bv * kt[r]);
+                        S[i] = fmaf(VEC ? dt[r] : at, S[i], bv * kt[r]);
                         acc[t] = fmaf(S[i], qt[r], acc[t]);
                     }
                 }
@@ -282,7 +298,7 @@ __global__ void __launch_bounds__(SC_THREADS) linear_scan_kernel(ScanArgs a) {
 // outputs meet in shared memory, added in the order of the warps.
 constexpr int SS_WARPS = 8;
 
-template <typename T, bool MLSTM>
+template <typename T, bool MLSTM, bool VEC>
 __global__ void __launch_bounds__(SS_WARPS * 32) linear_scan_single_kernel(ScanArgs a) {
     pdl_launch_dependents();
     extern __shared__ float sm[];
@@ -290,6 +306,7 @@ __global__ void __launch_bounds__(SS_WARPS * 32) linear_scan_single_kernel(ScanA
     float* qs = sm;                              // [dk] rotated, scaled
     float* ks = qs + dk;                         // [dk]
     float* red = ks + dk;                        // [WARPS][32]
+    float* as = red + SS_WARPS * 32;             // channel decays: [dk]
     const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int col = blockIdx.z * 32 + lane;
     const bool live = col < dvx;
@@ -309,11 +326,15 @@ __global__ void __launch_bounds__(SS_WARPS * 32) linear_scan_single_kernel(ScanA
         }
         qs[j] = qv * a.q_scale;
         ks[j] = kv * a.k_scale;
+        if (VEC) {
+            const float z = a.decay_pre[(size_t)row * a.decay_stride + h * dk + j] + (a.decay_bias ? a.decay_bias[h * dk + j] : 0.f);
+            as[j] = expf(log_sigmoid(z) * a.inv_tau);
+        }
     }
     float v = 0.f;
     if (col < dv) v = scan_in(to_f32(x[a.v_off + h * dv + col]), a.in_act);
     else if (MLSTM && col == dv) v = 1.f;
-    float keep = MLSTM ? 0.f : a.decay[h], m_new = 0.f;
+    float keep = (MLSTM || VEC) ? 0.f : a.decay[h], m_new = 0.f;
     if (MLSTM) {
         const float cap = a.gate_cap;
         const float* g = a.gate_pre + (size_t)row * 2 * H;
@@ -331,7 +352,7 @@ __global__ void __launch_bounds__(SS_WARPS * 32) linear_scan_single_kernel(ScanA
 #pragma unroll 4
         for (int r = warp; r < dk; r += SS_WARPS) {
             float* sp = st + (size_t)r * dvx + col;
-            const float s_new = fmaf(keep, *sp, v * ks[r]);
+            const float s_new = fmaf(VEC ? as[r] : keep, *sp, v * ks[r]);
             *sp = s_new;
             acc = fmaf(s_new, qs[r], acc);
         }
@@ -347,29 +368,29 @@ __global__ void __launch_bounds__(SS_WARPS * 32) linear_scan_single_kernel(ScanA
     }
 }
 
-template <typename T, bool MLSTM>
+template <typename T, bool MLSTM, bool VEC>
 static int scan_single_launch(const ScanArgs& a, int B, cudaStream_t stream) {
     const int dvx = a.dv + (MLSTM ? 1 : 0);
-    const size_t smem = (size_t)(2 * a.dk + SS_WARPS * 32) * sizeof(float);
-    return launch_pdl(linear_scan_single_kernel<T, MLSTM>, dim3(B, a.H, (dvx + 31) / 32), dim3(SS_WARPS * 32), smem, stream, a);
+    const size_t smem = (size_t)(2 * a.dk + SS_WARPS * 32 + (VEC ? a.dk : 0)) * sizeof(float);
+    return launch_pdl(linear_scan_single_kernel<T, MLSTM, VEC>, dim3(B, a.H, (dvx + 31) / 32), dim3(SS_WARPS * 32), smem, stream, a);
 }
 
-template <typename T, bool MLSTM>
+template <typename T, bool MLSTM, bool VEC>
 static int scan_launch(const ScanArgs& a, int B, cudaStream_t stream) {
     const int dvx = a.dv + (MLSTM ? 1 : 0);
     dim3 grid(B, a.H, (dvx + SC_COLS - 1) / SC_COLS);
     const size_t smem = (size_t)(4 * SC_CHUNK * a.dk + 2 * SC_CHUNK * SC_COLS + 4 * SC_CHUNK + 1 +
-                                 (a.dk + 1) * (SC_COLS + 1)) * sizeof(float);      // a little more than the kernel lays out
+                                 (a.dk + 1) * (SC_COLS + 1) + (VEC ? 2 * SC_CHUNK * a.dk : 0)) * sizeof(float);      // a little more than the kernel lays out
     auto go = [&](auto kernel) {
         if (smem > 48 * 1024 &&
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return lq_launch_status();
         return launch_pdl(kernel, grid, dim3(SC_THREADS), smem, stream, a);
     };
-    if (a.dk <= 1 * SC_R) return go(linear_scan_kernel<T, 1, MLSTM>);
-    if (a.dk <= 2 * SC_R) return go(linear_scan_kernel<T, 2, MLSTM>);
-    if (a.dk <= 4 * SC_R) return go(linear_scan_kernel<T, 4, MLSTM>);
-    if (a.dk <= 8 * SC_R) return go(linear_scan_kernel<T, 8, MLSTM>);
+    if (a.dk <= 1 * SC_R) return go(linear_scan_kernel<T, 1, MLSTM, VEC>);
+    if (a.dk <= 2 * SC_R) return go(linear_scan_kernel<T, 2, MLSTM, VEC>);
+    if (a.dk <= 4 * SC_R) return go(linear_scan_kernel<T, 4, MLSTM, VEC>);
+    if (a.dk <= 8 * SC_R) return go(linear_scan_kernel<T, 8, MLSTM, VEC>);
     return LQ_BAD_SIZE;
 }
 
@@ -378,27 +399,29 @@ LQ_EXPORT int lq_linear_scan(const void* qkv, int dtype, int stride, int q_off, 
                              const float* gate_bias, float gate_cap, const float* decay, float q_scale, float k_scale,
                              float* state, long long slot_stride, const int* cu_rows, const int* slots, float* out,
                              float* exp_neg_m, int B, int H, int dk, int dv, int mlstm, int single, int in_act,
+                             const float* decay_pre, int decay_stride, const float* decay_bias, float inv_tau,
                              cudaStream_t stream) {
     if (B <= 0) return LQ_OK;
     if (in_act < 0 || in_act > 1) return LQ_BAD_SIZE;
     if (rot % 2 || rot > dk || (rot && (!cos_t || !sin_t))) return LQ_BAD_SIZE;
-    if (mlstm ? (!gate_pre || !gate_bias || !exp_neg_m) : !decay) return LQ_BAD_SIZE;
+    const bool vec = decay_pre != nullptr;          // a decay per key channel and token instead of one per head
+    if (mlstm ? (!gate_pre || !gate_bias || !exp_neg_m || vec) : (!decay && !vec)) return LQ_BAD_SIZE;
     ScanArgs a{qkv, stride, q_off, k_off, v_off, cos_t, sin_t, rot, tok_pos, gate_pre, gate_bias, gate_cap, decay,
-               q_scale, k_scale, state, slot_stride, cu_rows, slots, out, exp_neg_m, H, dk, dv, in_act};
+               q_scale, k_scale, state, slot_stride, cu_rows, slots, out, exp_neg_m, H, dk, dv, in_act,
+               decay_pre, decay_stride, decay_bias, inv_tau};
+    typedef __nv_bfloat16 bf;
+    if (dtype != LQ_F32 && dtype != LQ_BF16) return LQ_BAD_DTYPE;
+    const bool f32 = dtype == LQ_F32;
     if (single) {
         // Every sequence brings exactly one token (row cu_rows[b]).
         if (dk > 256) return LQ_BAD_SIZE;
-        if (dtype == LQ_F32)
-            return mlstm ? scan_single_launch<float, true>(a, B, stream) : scan_single_launch<float, false>(a, B, stream);
-        if (dtype == LQ_BF16)
-            return mlstm ? scan_single_launch<__nv_bfloat16, true>(a, B, stream)
-                         : scan_single_launch<__nv_bfloat16, false>(a, B, stream);
-        return LQ_BAD_DTYPE;
+        if (mlstm) return f32 ? scan_single_launch<float, true, false>(a, B, stream) : scan_single_launch<bf, true, false>(a, B, stream);
+        if (vec) return f32 ? scan_single_launch<float, false, true>(a, B, stream) : scan_single_launch<bf, false, true>(a, B, stream);
+        return f32 ? scan_single_launch<float, false, false>(a, B, stream) : scan_single_launch<bf, false, false>(a, B, stream);
     }
-    if (dtype == LQ_F32) return mlstm ? scan_launch<float, true>(a, B, stream) : scan_launch<float, false>(a, B, stream);
-    if (dtype == LQ_BF16)
-        return mlstm ? scan_launch<__nv_bfloat16, true>(a, B, stream) : scan_launch<__nv_bfloat16, false>(a, B, stream);
-    return LQ_BAD_DTYPE;
+    if (mlstm) return f32 ? scan_launch<float, true, false>(a, B, stream) : scan_launch<bf, true, false>(a, B, stream);
+    if (vec) return f32 ? scan_launch<float, false, true>(a, B, stream) : scan_launch<bf, false, true>(a, B, stream);
+    return f32 ? scan_launch<float, false, false>(a, B, stream) : scan_launch<bf, false, false>(a, B, stream);
 }
 
 // ------------------------------------------------------------------ per-head unit norm, weight and gate

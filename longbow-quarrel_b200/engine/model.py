@@ -27,6 +27,7 @@ class Model:
         for n, entry in enumerate(spec.schedule):
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {n} names layer {entry.layer}; the model has {len(self.blocks)}")
+        self._keeps_embedding = any(getattr(b, "reads_embedding", False) for b in self.blocks)
         writers = [e.cache for e in spec.schedule if e.writes_cache]
         if len(set(writers)) != len(writers):
             raise ValueError("schedule: two runs write the same cache entry")
@@ -132,9 +133,17 @@ class Model:
         probe = self.probe
         if probe is not None:
             probe(-1, x, ctx)
+        # A block that reads the embedding's rows again later (`reads_embedding`) gets a copy: the stream changes in place.
+        embedded = x.clone() if self._keeps_embedding else None
         normed = None           # rows of the next layer's first norm, when this layer's last product made them
         for i, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
+            if getattr(block, "replaces_stream", False):
+                # A block that makes a new stream out of the old one (and the embedding's rows); it is no layer, and
+                # the probe is not called for it.
+                x = block.forward(x, ctx, embedded=embedded)
+                normed = None
+                continue
             if i in states:
                 # A block with state of its own (it folds no norms: what the layer ahead left unfinished is finished first).
                 block.forward(x, ctx, cache.view(entry.cache), entry.writes_cache, state=cache.view(states[i][0]))

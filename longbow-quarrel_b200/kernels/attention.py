@@ -55,7 +55,7 @@ def decode_work_size(B: int, teams: int) -> int:
     return teams + 1 + 5 * teams
 
 
-def cut_decode_work(positions, window: int, teams: int, max_parts: int = MAX_SPLITS, keep_first: int = 0) -> np.ndarray:
+def cut_decode_work(positions, window: int, teams: int, max_parts: int = MAX_SPLITS, keep_first: int = 0, chunk: int = 0) -> np.ndarray:
     """The decode kernel's work list for tokens at these positions: every token's keys cut into parts of
     nearly the same length for all tokens, as short as `teams` parts in all allow, so that a long sequence
     gets more parts than a short one and the blocks finish together (with the same number of slices for
@@ -64,13 +64,17 @@ def cut_decode_work(positions, window: int, teams: int, max_parts: int = MAX_SPL
     each, or none), then (token, first tile, last tile + 1, part, parts of the token) per segment, in the
     kernel's 16-key tiles counted from the first one the token sees (its window's first tile; with
     `keep_first`, the tiles of the kept first positions that lie ahead of the window are counted before the
-    window's).  No part is shorter than MIN_PART_TILES unless it is a whole token, and no token gets more
+    window's).  With `chunk` n instead of a window, a token's first tile is the one that holds the first position of
+    its block of n positions.  No part is shorter than MIN_PART_TILES unless it is a whole token, and no token gets more
     than max_parts."""
     pos = np.asarray(positions, dtype=np.int64)
     B = len(pos)
     if teams < B:
         raise ValueError(f"{B} tokens need at least as many teams, not {teams}")
-    first = np.where((window > 0) & (pos >= window), pos - window + 1, 0) // DECODE_TILE
+    if chunk > 0:
+        first = (pos - pos % chunk) // DECODE_TILE
+    else:
+        first = np.where((window > 0) & (pos >= window), pos - window + 1, 0) // DECODE_TILE
     if window > 0 and keep_first > 0:
         first = first - np.minimum(-(-keep_first // DECODE_TILE), first)       # the kept tiles count as well
     tiles = pos // DECODE_TILE + 1 - first
@@ -94,9 +98,9 @@ def cut_decode_work(positions, window: int, teams: int, max_parts: int = MAX_SPL
     return out
 
 
-def decode_work(H: int, Hkv: int, window: int | None, device, hd: int = 128, keep_first: int = 0):
-    """Builder of the decode kernel's work list for attention of these head counts, this window and these kept
-    first positions: empty for a step with prompts."""
+def decode_work(H: int, Hkv: int, window: int | None, device, hd: int = 128, keep_first: int = 0, chunk: int | None = None):
+    """Builder of the decode kernel's work list for attention of these head counts, this window (or these blocks of
+    positions) and these kept first positions: empty for a step with prompts."""
     group_tiles = -(-(H // Hkv) // 16)
 
     def build(step) -> np.ndarray:
@@ -104,13 +108,13 @@ def decode_work(H: int, Hkv: int, window: int | None, device, hd: int = 128, kee
             return np.zeros(0, dtype=np.int32)
         return cut_decode_work(np.asarray(step.past), int(window or 0),
                                decode_teams(step.B, Hkv, group_tiles, resident_blocks(device, hd)),
-                               keep_first=int(keep_first or 0))
+                               keep_first=int(keep_first or 0), chunk=int(chunk or 0))
     return build
 
 
-def decode_work_name(H: int, Hkv: int, window: int | None, keep_first: int = 0) -> str:
+def decode_work_name(H: int, Hkv: int, window: int | None, keep_first: int = 0, chunk: int | None = None) -> str:
     kept = int(keep_first or 0) if window else 0
-    return f"decode_work:{H}:{Hkv}:{int(window or 0)}" + (f":{kept}" if kept else "")
+    return f"decode_work:{H}:{Hkv}:{ops.span(window, chunk)}" + (f":{kept}" if kept else "")
 
 
 PREFILL_LISTS = {"query_blocks64": query_blocks(64), "query_blocks128": query_blocks(128)}
@@ -134,14 +138,14 @@ def decode_kernel(dtype: torch.dtype, hd: int) -> bool:
 
 
 def step_needs(dtype: torch.dtype, hd: int, H: int | None = None, Hkv: int | None = None, window: int | None = None,
-               device=None, keep_first: int = 0) -> dict:
+               device=None, keep_first: int = 0, chunk: int | None = None) -> dict:
     """The work lists that attention of this dtype and head size reads: the query blocks of steps with
     prompts, and (when the head counts are given) the balanced segments of steps of single tokens."""
     kind = prefill_kernel(dtype, hd)
     name = {"tc": "query_blocks128", "mma": "query_blocks64"}.get(kind)
     needs = {name: PREFILL_LISTS[name]} if name else {}
     if H is not None and Hkv and BALANCED_DECODE and decode_kernel(dtype, hd):
-        needs[decode_work_name(H, Hkv, window, keep_first)] = decode_work(H, Hkv, window, device, hd, keep_first)
+        needs[decode_work_name(H, Hkv, window, keep_first, chunk)] = decode_work(H, Hkv, window, device, hd, keep_first, chunk)
     return needs
 
 
@@ -153,64 +157,70 @@ def _blocks(ctx, name):
 
 
 def attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w=None, vd=None, sink=None, gate=None, softcap=None,
-              keep_first=0):
+              keep_first=0, chunk=None, gate_per_head=False):
     """Rows of qkv hold q in their left H*hd columns.  Returns [T, H*vd].  next_w: the weights the
     stream reads after the attention (the decode kernel asks for their first bytes as it ends).
     vd: size of a value head (default hd); sink: float32 [H], one more term of each head's softmax
     denominator; gate: [T, H*vd] whose sigmoid multiplies the output; softcap c: score <- c tanh(score / c);
-    keep_first n: with a window, a sequence's first n positions stay visible."""
+    keep_first n: with a window, a sequence's first n positions stay visible.  chunk n (instead of a window): a position
+    sees only its own block of n positions.  gate_per_head: the gate is [T, H], one number for a head's values."""
     vd = vd or hd
     keep_first = int(keep_first or 0) if window else 0
     if vd != hd:
-        return general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate, softcap, keep_first)
-    out = _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, gate, softcap, keep_first)
+        return general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate, softcap, keep_first, chunk,
+                                 gate_per_head)
+    out = _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, gate, softcap, keep_first, chunk)
     if gate is not None and out is not None:
-        return ops.gate_mul(out, gate, "sigmoid")         # the tensor-core kernels leave the gate to a kernel of its own
+        # The tensor-core kernels leave the gate to a kernel of its own.
+        return ops.gate_mul(out, gate, "sigmoid", group=vd if gate_per_head else 1)
     return out if out is not None else general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate,
-                                                         softcap, keep_first)
+                                                         softcap, keep_first, chunk, gate_per_head)
 
 
-def _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, gate, softcap=None, keep_first=0):
+def _attention(qkv, cache_view, ctx, H, Hkv, hd, scale, window, next_w, sink, gate, softcap=None, keep_first=0, chunk=None):
     """The tensor-core kernels where they take the sizes; None where only the plain kernel does and a gate
     is to be applied (the plain kernel applies it itself)."""
     aligned = qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0
     more = dict(sink=sink, softcap=softcap, keep_first=keep_first)
+    mask = ops.span(window, chunk)          # the kernels take a window as w and blocks of n positions as -n
     if not ctx.decode and aligned:
         kind = prefill_kernel(qkv.dtype, hd, cache_view.page_size)
         if kind == "tc":
             blocks = _blocks(ctx, "query_blocks128")
             if blocks is not None:
                 return ops.attn_prefill_tc(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.slots,
-                                           ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, window, **more)
+                                           ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, mask, **more)
             kind = "mma" if "query_blocks64" in ctx.extra else None
         if kind == "mma":
             blocks = _blocks(ctx, "query_blocks64")
             if blocks is not None:
                 return ops.attn_prefill(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.slots,
-                                        ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, window, **more)
+                                        ctx.kv_len, blocks, H, Hkv, hd, cache_view.page_size, scale, mask, **more)
     if ctx.decode and aligned and decode_kernel(qkv.dtype, hd) and cache_view.page_size % 16 == 0:
-        work = ctx.extra.get(decode_work_name(H, Hkv, window, keep_first))
+        work = ctx.extra.get(decode_work_name(H, Hkv, window, keep_first, chunk))
         if work is not None and work.numel():
             teams = decode_teams(ctx.T, Hkv, -(-(H // Hkv) // 16), resident_blocks(qkv.device, hd))
             if work.numel() == decode_work_size(ctx.T, teams):
                 return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
-                                       ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window,
+                                       ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, mask,
                                        min(MAX_SPLITS, teams), next_w=next_w, early_loads=True, work=work, teams=teams,
                                        **more)
         n_splits = decode_splits(ctx.T, Hkv, -(-(H // Hkv) // 16), ctx.max_kv, resident_blocks(qkv.device, hd))
         return ops.attn_decode(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
-                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, n_splits,
+                               ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, mask, n_splits,
                                next_w=next_w, early_loads=True, **more)      # a decode step: one new token per sequence
     if gate is not None:
         return None
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, sink=sink,
-                               softcap=softcap, keep_first=keep_first)
+                               softcap=softcap, keep_first=keep_first, chunk=chunk)
 
 
-def general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate, softcap=None, keep_first=0):
-    """Attention through the plain kernel, which takes every option: a sink, a gate, values of another size than the
-    keys, capped scores, kept first positions."""
+def general_attention(qkv, cache_view, ctx, H, Hkv, hd, vd, scale, window, sink, gate, softcap=None, keep_first=0, chunk=None,
+                      gate_per_head=False):
+    """Attention through the plain kernel, which takes every option: a sink, a gate (per value or per head), values of
+    another size than the keys, capped scores, kept first positions, blocks of positions."""
     return ops.attention_plain(qkv, cache_view.k_pages, cache_view.v_pages, cache_view.page_table, ctx.tok_pos,
                                ctx.tok_seq, ctx.slots, H, Hkv, hd, cache_view.page_size, scale, window, vd=vd,
-                               sink=sink, gate=gate, softcap=softcap, keep_first=keep_first)
+                               sink=sink, gate=gate, softcap=softcap, keep_first=keep_first, chunk=chunk,
+                               gate_per_head=gate_per_head)

@@ -240,6 +240,40 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: torch.dt
     return out
 
 
+def layernorm(x: torch.Tensor, gain: torch.Tensor, bias: torch.Tensor | None, eps: float, out_dtype: torch.dtype,
+              rows: torch.Tensor | None = None, add: tuple = ()) -> torch.Tensor:
+    """Layer norm of rows of the float32 stream x [T, D]: (x - mean) / sqrt(var + eps) * gain + bias, var the mean of the
+    squared deviations, all in 32-bit; `rows` (int32) picks rows.  add = ((y, m), ...) (one or two float32 [T, D]): the
+    stream first takes x += m * y for each, in place, in the same pass."""
+    if x.dtype != torch.float32 or gain.dtype != torch.float32 or (bias is not None and bias.dtype != torch.float32):
+        raise KernelError("layernorm reads a float32 stream, float32 gains and biases")
+    D = x.shape[-1]
+    n = x.shape[0] if rows is None else rows.numel()
+    if len(add) > 2 or (add and rows is not None):
+        raise KernelError("layernorm: at most two branches join the stream, and only when every row is normed")
+    for y, _ in add:
+        if y.dtype != torch.float32 or y.shape != x.shape or not y.is_contiguous():
+            raise KernelError("layernorm: a branch must be contiguous float32 of the stream's shape")
+    (y1, m1), (y2, m2) = (tuple(add) + ((None, 0.0), (None, 0.0)))[:2]
+    out = torch.empty((n, D), dtype=out_dtype, device=x.device)
+    fn = _fn("plain_kernels", "lq_layernorm", [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_p(_contig(x, "x")), _p(y1), float(m1), _p(y2), float(m2), _p(gain), _p(bias), _p(rows), _p(out),
+              dtype_code(out_dtype), n, D, float(eps), _stream()), "layernorm")
+    return out
+
+
+def side_by_side(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """[a, b] along the columns, in out_dtype, from two contiguous float32 [T, D]: the input of a product that reads two streams."""
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or a.shape != b.shape or not a.is_contiguous() or not b.is_contiguous():
+        raise KernelError("side_by_side: two contiguous float32 tensors of one shape")
+    T, D = a.shape
+    out = torch.empty((T, 2 * D), dtype=out_dtype, device=a.device)
+    fn = _fn("plain_kernels", "lq_side_by_side", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(a), _p(b), _p(out), dtype_code(out_dtype), T, D, _stream()), "side_by_side")
+    return out
+
+
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, residual: torch.Tensor | None = None,
                out: torch.Tensor | None = None) -> torch.Tensor:
     """a [M, K] . w [N, K]^T (+ residual) on the CUDA cores, every product in float32."""
@@ -299,31 +333,45 @@ def rope_kv_write(qkv: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor
 def attention_plain(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq, slots, H: int, Hkv: int,
                     hd: int, page_size: int, scale: float, window: int | None,
                     out: torch.Tensor | None = None, vd: int | None = None, sink: torch.Tensor | None = None,
-                    gate: torch.Tensor | None = None, softcap: float | None = None, keep_first: int = 0) -> torch.Tensor:
+                    gate: torch.Tensor | None = None, softcap: float | None = None, keep_first: int = 0,
+                    chunk: int | None = None, gate_per_head: bool = False) -> torch.Tensor:
     """Causal attention of every token over its own sequence's cache; q is the left
     H*hd columns of a [T, q_stride] buffer.  softcap c: score <- c tanh(score / c) after the scale.  keep_first: with a
     window, the sequence's first keep_first positions stay visible when the window has moved past them.  vd: size of a value head (default hd).  sink: float32 [H], one
     more term exp(sink) in each head's softmax denominator.  gate: a [T, H*vd] view (rows may be strided) whose
-    sigmoid multiplies the output."""
+    sigmoid multiplies the output; with gate_per_head a [T, H] view, one number for all values of a head.
+    chunk n (instead of a window): a position sees only its own block of n positions."""
     T = q.shape[0]
     vd = vd or hd
     if hd > 256 or vd > 256:
         raise KernelError(f"attention: head sizes {hd}, {vd} exceed 256")
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != H):
         raise KernelError("attention: sink must be float32 [H]")
-    if gate is not None and (gate.dtype not in (q.dtype, torch.float32) or gate.shape != (T, H * vd) or gate.stride(1) != 1):
-        raise KernelError("attention: the gate must be [T, H * vd] of the queries' dtype or float32, with unit column stride")
+    if gate is not None and (gate.dtype not in (q.dtype, torch.float32) or gate.stride(1) != 1
+                             or gate.shape != (T, H if gate_per_head else H * vd)):
+        raise KernelError("attention: the gate must be [T, H * vd] (or [T, H]) of the queries' dtype or float32, with unit column stride")
     if out is None:
         out = torch.empty((T, H * vd), dtype=q.dtype, device=q.device)
     fn = _fn("plain_kernels", "lq_attention_plain", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                      c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
-                                                     c_void_p])
+                                                     c_int, c_void_p])
     _check(fn(_p(q), q.stride(0), dtype_code(q), _p(k_pages), _p(v_pages), _p(page_table), page_table.stride(0),
               _p(tok_pos), _p(tok_seq), _p(slots), _p(out), T, H, Hkv, hd, page_size, float(scale),
-              int(window or 0), vd, _p(sink), _p(gate), gate.stride(0) if gate is not None else 0,
-              dtype_code(gate) if gate is not None else F32, float(softcap or 0.0), int(keep_first or 0), _stream()), "attention")
+              span(window, chunk), vd, _p(sink), _p(gate), gate.stride(0) if gate is not None else 0,
+              dtype_code(gate) if gate is not None else F32, float(softcap or 0.0), int(keep_first or 0),
+              int(bool(gate_per_head and gate is not None)), _stream()), "attention")
     return out
+
+
+def span(window: int | None, chunk: int | None = None) -> int:
+    """A mask as the one integer the attention kernels take: a sliding window of w positions as w, blocks of n
+    positions (a position sees its own block only) as -n, every earlier position as 0."""
+    if chunk:
+        if window:
+            raise KernelError("attention: a window or blocks of positions, not both")
+        return -int(chunk)
+    return int(window or 0)
 
 
 def swiglu(gu: torch.Tensor, block: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -386,13 +434,18 @@ def rmsnorm_add(y: torch.Tensor, gain: torch.Tensor, eps: float, x: torch.Tensor
 
 def rope_partial(buf: torch.Tensor, bias: torch.Tensor | None, cos, sin, rot: int, tok_pos, tok_seq, slots,
                  page_table, k_pages, v_pages, n_rot: int, k_first: int, Hkv: int, hd: int, vd: int, v_off: int,
-                 page_size: int, qout: torch.Tensor | None = None, v_unit_eps: float | None = None) -> None:
+                 page_size: int, qout: torch.Tensor | None = None, v_unit_eps: float | None = None,
+                 unit_norm: str | None = None, norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0,
+                 q_temp: tuple | None = None) -> None:
     """Biases, then rotation of the first `rot` dimensions, for each of the n_rot heads at the left of buf's rows;
     heads below k_first (queries) go to `qout` [T, k_first * hd] (default: back in place), heads k_first.. into
     k_pages and the values at column v_off into v_pages where a cache is given.  bias: float32 over buf's
     columns, or None; cos/sin: float32 [positions, rot / 2].  buf may be float32 while qout and the cache are
     bfloat16 (a product's 32-bit sums, rounded once, after bias and rotation).  v_unit_eps: each value head is divided by
-    its root mean square, sqrt(mean(v^2) + v_unit_eps), before it is stored."""
+    its root mean square, sqrt(mean(v^2) + v_unit_eps), before it is stored.  unit_norm (32-bit, after the bias and ahead
+    of the rotation): "head", every one of the n_rot heads over its own root mean square sqrt(mean(x^2) + norm_eps);
+    "all", the queries over the root mean square of all of them together and the keys likewise, times norm_weight
+    (float32 over the n_rot * hd columns).  q_temp = (coef, every): the queries times 1 + coef ln(floor((p + 1) / every) + 1)."""
     T = buf.shape[0]
     if buf.stride(1) != 1:
         raise KernelError("rope_partial: rows must be contiguous")
@@ -408,13 +461,23 @@ def rope_partial(buf: torch.Tensor, bias: torch.Tensor | None, cos, sin, rot: in
         raise KernelError("rope_partial: the bias must be float32 over the rows' columns")
     if k_pages is not None and (k_pages.dtype != qout.dtype or v_pages.dtype != qout.dtype):
         raise KernelError("rope_partial: the cache and the queries must have one dtype")
+    if unit_norm not in (None, "head", "all"):
+        raise KernelError(f"rope_partial: unit_norm {unit_norm!r} is not one of None, 'head', 'all'")
+    mode = {None: 0, "head": 1, "all": 2}[unit_norm]
+    if norm_weight is not None and (mode != 2 or norm_weight.dtype != torch.float32 or norm_weight.numel() != n_rot * hd
+                                    or not norm_weight.is_contiguous()):
+        raise KernelError("rope_partial: the norm's weight goes with unit_norm 'all' and is contiguous float32 over the heads' columns")
+    if q_temp is not None and not int(q_temp[1]) > 0:
+        raise KernelError("rope_partial: the query temperature's step must be positive")
     fn = _fn("plain_kernels", "lq_rope_partial", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                  c_int, c_void_p, c_float, c_float, c_int, c_void_p])
     _check(fn(_p(buf), dtype_code(buf), buf.stride(0), _p(qout), dtype_code(qout), qout.stride(0), _p(bias), _p(cos), _p(sin),
               int(rot), _p(tok_pos), _p(tok_seq), _p(slots), _p(page_table),
               page_table.stride(0) if page_table is not None else 0, _p(k_pages), _p(v_pages),
               T, n_rot, k_first, Hkv, hd, vd, v_off, page_size, int(v_unit_eps is not None), float(v_unit_eps or 0.0),
+              mode, _p(norm_weight), float(norm_eps), float(q_temp[0]) if q_temp else 0.0, int(q_temp[1]) if q_temp else 0,
               _stream()), "rope_partial")
 
 
@@ -441,14 +504,16 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
-def gate_mul(x: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid") -> torch.Tensor:
-    """x *= act(gate) in place; x [rows, cols] contiguous, gate a [rows, cols] view whose rows may be strided."""
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid", group: int = 1) -> torch.Tensor:
+    """x *= act(gate) in place; x [rows, cols] contiguous, gate a [rows, cols / group] view whose rows may be strided:
+    one gate for every `group` neighbouring columns (group = a head's size: one number per head)."""
     rows, cols = x.shape
-    if gate.dtype not in (x.dtype, torch.float32) or tuple(gate.shape) != (rows, cols) or gate.stride(1) != 1:
-        raise KernelError("gate_mul: the gate must have x's shape, x's dtype or float32, and unit column stride")
-    fn = _fn("plain_kernels", "lq_gate_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_p(_contig(x, "x")), _p(gate), gate.stride(0), dtype_code(x), dtype_code(gate), rows, cols, GATES[act], _stream()),
-           "gate_mul")
+    if group < 1 or cols % group or gate.dtype not in (x.dtype, torch.float32) or tuple(gate.shape) != (rows, cols // group) \
+            or gate.stride(1) != 1:
+        raise KernelError("gate_mul: the gate must be [rows, cols / group] of x's dtype or float32, with unit column stride")
+    fn = _fn("plain_kernels", "lq_gate_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_p(_contig(x, "x")), _p(gate), gate.stride(0), dtype_code(x), dtype_code(gate), rows, cols, GATES[act], int(group),
+              _stream()), "gate_mul")
     return x
 
 
@@ -776,7 +841,7 @@ def moe_down(u: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: 
 def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, cu_rows, slots, tok_pos,
                 B: int, H: int, dk: int, dv: int, q_scale: float = 1.0, k_scale: float = 1.0,
                 decay: torch.Tensor | None = None, gates: tuple | None = None, rot: tuple | None = None,
-                single: bool = False, in_act: str | None = None):
+                single: bool = False, in_act: str | None = None, channel_decay: tuple | None = None):
     """S_t = a_t S_(t-1) + b_t k_t v_t^T, o_t = S_t^T q_t for the rows of B sequences (rows cu_rows[b] ..
     cu_rows[b+1] of qkv belong to the sequence in slot slots[b]), from and into `state` (float32
     [slots, H, dk (+1), dv (+1)]).  decay: float32 [H] (a_t fixed, b_t = 1).  gates = (pre [rows, 2H] float32,
@@ -784,8 +849,10 @@ def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: to
     has one more row (the maximum) and one more column (the normaliser).  rot = (cos, sin, dims): q and k are
     rotated as they are read.  single: every sequence brings exactly one token (the kernel then streams the
     state once, without staging chunks of tokens).  in_act "silu": q, k and v each pass through silu, in float32, as
-    they are read.  Returns the raw outputs float32 [rows, H, dv (+1)] and,
-    with gates, exp(-maximum) float32 [rows, H]."""
+    they are read.  channel_decay = (pre, bias, tau): a decay for every key channel and token instead of one per head,
+    a_t[h, r] = sigmoid(pre[t, h * dk + r] + bias[h * dk + r])^(1 / tau), the rows of the state that belong to channel r
+    decaying by it; pre is a float32 [rows, H * dk] view (rows may be strided), bias float32 [H * dk] or None.
+    Returns the raw outputs float32 [rows, H, dv (+1)] and, with gates, exp(-maximum) float32 [rows, H]."""
     rows = qkv.shape[0]
     mlstm = gates is not None
     dvx, dkx = dv + int(mlstm), dk + int(mlstm)
@@ -793,8 +860,13 @@ def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: to
         raise KernelError(f"linear_scan: the state must be contiguous float32 [slots, {H}, {dkx}, {dvx}]")
     if qkv.stride(1) != 1:
         raise KernelError("linear_scan: rows must be contiguous")
-    if (decay is None) == (gates is None):
-        raise KernelError("linear_scan takes either a fixed decay or gates")
+    if (decay is not None) + (gates is not None) + (channel_decay is not None) != 1:
+        raise KernelError("linear_scan takes a fixed decay, gates or channel decays: one of them")
+    d_pre, d_bias, tau = channel_decay if channel_decay is not None else (None, None, 1.0)
+    if d_pre is not None and (d_pre.dtype != torch.float32 or tuple(d_pre.shape) != (rows, H * dk) or d_pre.stride(1) != 1
+                              or (d_bias is not None and (d_bias.dtype != torch.float32 or d_bias.numel() != H * dk))
+                              or not tau > 0):
+        raise KernelError("linear_scan: channel decays are float32 [rows, H * dk] with a float32 bias [H * dk] and tau > 0")
     if dk > 256:
         raise KernelError(f"linear_scan: key size {dk} exceeds 256")
     out = torch.empty((rows, H, dvx), dtype=torch.float32, device=qkv.device)
@@ -809,11 +881,12 @@ def linear_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, state: to
     fn = _fn("recurrent", "lq_linear_scan", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_float, c_void_p,
                                              c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                             c_int, c_int, c_int, c_void_p])
+                                             c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p])
     _check(fn(_p(qkv), dtype_code(qkv), qkv.stride(0), q_off, k_off, v_off, _p(cos), _p(sin), int(dims), _p(tok_pos),
               _p(pre), _p(bias), float(cap), _p(decay), float(q_scale), float(k_scale), _p(state), state.stride(0),
               _p(cu_rows), _p(slots), _p(out), _p(enm), B, H, dk, dv, int(mlstm), int(single and rows == B),
-              {None: 0, "silu": 1}[in_act], _stream()),
+              {None: 0, "silu": 1}[in_act], _p(d_pre), d_pre.stride(0) if d_pre is not None else 0, _p(d_bias), 1.0 / float(tau),
+              _stream()),
            "linear_scan", 1, "linear_scan:single" if single and rows == B else None)
     return out, enm
 

@@ -1,8 +1,8 @@
-from . import attention, block, conv, dense_mlp, embedding, latent_attention, mlp, moe, norm, recurrent, rope  # noqa: F401  (registers the parts)
-from .base import (CacheNeed, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, Runtime, StateNeed, StepContext)
+from . import attention, block, conv, dense_mlp, embedding, latent_attention, mlp, moe, norm, recurrent, rope, side_by_side  # noqa: F401  (registers the parts)
+from .base import (CacheNeed, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, Runtime, SeveralNeeds, StateNeed, StepContext)
 from .registry import make_part, register_part, registered_parts
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
-__all__ = ["CacheNeed", "FeedForward", "KVNeed", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "StateNeed",
+__all__ = ["CacheNeed", "FeedForward", "KVNeed", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "SeveralNeeds", "StateNeed",
            "StepContext", "make_part", "register_part", "registered_parts", "LayerSpec", "ModelSpec",
            "PartSpec", "ScheduleEntry"]

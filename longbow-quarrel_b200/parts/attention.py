@@ -24,7 +24,14 @@ positions, when the window has moved past them); `value_norm_eps` (each value he
 root mean square, sqrt(mean(v^2) + eps), before it is cached); a position part with interleaved pairs
 (the rows of the query and key projections are reordered at load, `parts.rope.pair_order`); and
 `cache_window` / `cache_keep_first`, what the cache entry keeps when layers that read it see further
-than the layer that writes it (default: the layer's own window and kept positions).
+than the layer that writes it (default: the layer's own window and kept positions); `sink="one"` (the
+denominator's one more term is exp(0) = 1 for every head, no tensor); `gate="sigmoid_head"` (one gate per
+head, W_g of H rows: every value of a head times sigmoid of the head's number); `qk_norm` "head" (q and k each
+divided by its root mean square per head, sqrt(mean(x^2) + norm_eps), no weight) or "all" (one norm over the whole
+query projection and one over the whole key projection, each with a weight of that size), in 32-bit on the
+products' 32-bit sums, ahead of the rotation; `q_temp` (coef, every): the queries times
+1 + coef ln(floor((p + 1) / every) + 1) at position p; `chunk` n (instead of a window): position i sees j <= i
+only in its own block of n positions, floor(i / n) = floor(j / n), and the cache gives back the pages below it.
 """
 from __future__ import annotations
 
@@ -57,7 +64,8 @@ class Attention(Mixer):
                  own_kv: bool = True, names: dict | None = None, value_dim: int | None = None, bias: bool = False,
                  sink: bool = False, gate: str | None = None, softcap: float | None = None, keep_first: int = 0,
                  value_norm_eps: float | None = None, cache_window: int | None | str = "own",
-                 cache_keep_first: int | None = None):
+                 cache_keep_first: int | None = None, qk_norm: str | None = None, norm_eps: float = 0.0,
+                 q_temp: tuple | None = None, chunk: int | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if head_dim % 2 or not 2 <= head_dim <= 256:
@@ -70,9 +78,21 @@ class Attention(Mixer):
         self.vd = head_dim if value_dim is None else int(value_dim)
         if not 1 <= self.vd <= 256:
             raise ValueError(f"attention: value_dim {self.vd} must be at most 256")
-        if gate not in (None, "sigmoid"):
-            raise ValueError(f"attention: gate {gate!r} is not supported (supported: 'sigmoid')")
+        if gate not in (None, "sigmoid", "sigmoid_head"):
+            raise ValueError(f"attention: gate {gate!r} is not supported (supported: 'sigmoid', 'sigmoid_head')")
+        if qk_norm not in (None, "head", "all"):
+            raise ValueError(f"attention: qk_norm {qk_norm!r} is not supported (supported: 'head', 'all')")
+        if chunk is not None and (window is not None or int(chunk) < 1):
+            raise ValueError("attention: blocks of positions (chunk >= 1) or a window, not both")
+        if q_temp is not None and not int(q_temp[1]) > 0:
+            raise ValueError("attention: q_temp is (coef, every) with every >= 1")
         self.bias, self.sink, self.gate = bool(bias), bool(sink), gate
+        self.sink_learned = self.sink and sink != "one"
+        self.gate_per_head = gate == "sigmoid_head"
+        self.qk_norm, self.norm_eps = qk_norm, float(norm_eps)
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else None
+        self.chunk = int(chunk) if chunk is not None else None
+        self.norm_w = None
         self.softcap = float(softcap) if softcap else None
         self.keep_first = int(keep_first or 0) if window is not None else 0
         self.value_norm_eps = None if value_norm_eps is None else float(value_norm_eps)
@@ -85,24 +105,26 @@ class Attention(Mixer):
             self.names.setdefault(key + "_bias", self.names[key].replace(".weight", "") + ".bias")
         self.names.setdefault("sink", "sinks")
         self.names.setdefault("g", "g_proj.weight")
+        self.names.setdefault("q_norm", "q_norm.weight")
+        self.names.setdefault("k_norm", "k_norm.weight")
         self.position = make_part("position", position, runtime) if position is not None else None
         self.rot = getattr(self.position, "rotary_dims", head_dim) if self.position is not None else 0
         # The kernels that fuse rotation and cache write into the projections, and the tensor-core attention
         # kernels, know the plain form only; every option above takes the general kernels.
         self.general = self.bias or self.sink or self.gate is not None or self.vd != head_dim or \
             (self.position is not None and self.rot != head_dim) or self.softcap is not None or self.keep_first > 0 or \
-            self.value_norm_eps is not None
+            self.value_norm_eps is not None or self.qk_norm is not None or self.q_temp is not None or self.chunk is not None
         self.b_qkv = self.sinks = None
         self.w_qkv: linear.LinearWeight | None = None
         self.w_o: linear.LinearWeight | None = None
 
     def cache_need(self):
         return KVNeed(self.Hkv, self.hd, self.cache_window, self.vd if self.vd != self.hd else None,
-                      keep_first=self.cache_keep_first if self.cache_window is not None else 0)
+                      keep_first=self.cache_keep_first if self.cache_window is not None else 0, chunk=self.chunk)
 
     def step_needs(self):
         return attention_kernels.step_needs(self.runtime.act_dtype, self.hd, self.H, self.Hkv, self.window,
-                                            self.runtime.device, keep_first=self.keep_first)
+                                            self.runtime.device, keep_first=self.keep_first, chunk=self.chunk)
 
     def weights(self):
         n = self.names
@@ -115,10 +137,14 @@ class Attention(Mixer):
             if self.own_kv:
                 out[n["k_bias"]] = WeightSpec((self.Hkv * self.hd,), init="small", full_precision=True)
                 out[n["v_bias"]] = WeightSpec((self.Hkv * self.vd,), init="small", full_precision=True)
-        if self.sink:
+        if self.sink_learned:
             out[n["sink"]] = WeightSpec((self.H,), init=("uniform", 0.0, 4.0), full_precision=True)
         if self.gate is not None:
-            out[n["g"]] = WeightSpec((self.H * self.vd, self.D))
+            out[n["g"]] = WeightSpec((self.H if self.gate_per_head else self.H * self.vd, self.D))
+        if self.qk_norm == "all":
+            out[n["q_norm"]] = WeightSpec((self.H * self.hd,), init="gain", full_precision=True)
+            if self.own_kv:
+                out[n["k_norm"]] = WeightSpec((self.Hkv * self.hd,), init="gain", full_precision=True)
         if self.position is not None:
             out.update(self.position.weights())        # a position encoding may have tensors of its own
         return out
@@ -135,7 +161,7 @@ class Attention(Mixer):
         n = self.names
         tensors = dict(tensors)
         for key, heads in (("q", self.H), ("k", self.Hkv)):
-            for name in (n[key], n[key + "_bias"]):
+            for name in (n[key], n[key + "_bias"], n[key + "_norm"]):
                 if name in tensors and (key == "q" or self.own_kv):
                     tensors[name] = self._reordered(tensors[name], heads)
         rows = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
@@ -148,7 +174,11 @@ class Attention(Mixer):
             keys = ["q_bias"] + (["k_bias", "v_bias"] if self.own_kv else [])
             self.b_qkv = torch.cat([tensors[n[k]].to(torch.float32) for k in keys]).contiguous()
         if self.sink:
-            self.sinks = tensors[n["sink"]].to(torch.float32).contiguous()
+            self.sinks = tensors[n["sink"]].to(torch.float32).contiguous() if self.sink_learned else \
+                torch.zeros(self.H, dtype=torch.float32, device=self.runtime.device)
+        if self.qk_norm == "all":
+            keys = ["q_norm"] + (["k_norm"] if self.own_kv else [])
+            self.norm_w = torch.cat([tensors[n[k]].to(torch.float32) for k in keys]).contiguous()
         self.w_o = linear.LinearWeight(tensors[n["o"]])
         if self.position is not None and self.position.weights():
             self.position.load({name: tensors[name] for name in self.position.weights()})
@@ -159,9 +189,9 @@ class Attention(Mixer):
         denominator and the gate on the way out; the output projection."""
         H, G, hd, vd = self.H, self.Hkv, self.hd, self.vd
         act = self.runtime.act_dtype
-        # With biases the product hands on its 32-bit sums: bias and rotation meet them before anything is
-        # rounded, as if the bias were added inside the product.
-        wide = self.bias and act != torch.float32
+        # With biases (or norms of q and k) the product hands on its 32-bit sums: bias, norm and rotation meet them
+        # before anything is rounded, as if they were done inside the product.
+        wide = (self.bias or self.qk_norm is not None) and act != torch.float32
         rows = linear.linear(h, self.w_qkv, torch.float32 if wide else act)
         q = torch.empty((rows.shape[0], H * hd), dtype=act, device=rows.device) if wide else rows
         tables = self.position.tables() if self.position is not None else None
@@ -172,12 +202,13 @@ class Attention(Mixer):
         ops.rope_partial(rows, self.b_qkv, cos, sin, self.rot if tables is not None else 0, ctx.tok_pos, ctx.tok_seq,
                          ctx.slots, cache_view.page_table if store else None, cache_view.k_pages if store else None,
                          cache_view.v_pages if store else None, H + (G if self.own_kv else 0), H, G, hd, vd, v_off,
-                         cache_view.page_size, qout=q if wide else None, v_unit_eps=self.value_norm_eps)
+                         cache_view.page_size, qout=q if wide else None, v_unit_eps=self.value_norm_eps,
+                         unit_norm=self.qk_norm, norm_weight=self.norm_w, norm_eps=self.norm_eps, q_temp=self.q_temp)
         g_off = H * hd + (G * (hd + vd) if self.own_kv else 0)
-        gate = rows[:, g_off:g_off + H * vd] if self.gate is not None else None
+        gate = rows[:, g_off:g_off + (H if self.gate_per_head else H * vd)] if self.gate is not None else None
         out = attention_kernels.attention(q, cache_view, ctx, H, G, hd, self.scale, self.window,
                                           next_w=self.w_o.tensor, vd=vd, sink=self.sinks, gate=gate, softcap=self.softcap,
-                                          keep_first=self.keep_first)
+                                          keep_first=self.keep_first, chunk=self.chunk, gate_per_head=self.gate_per_head)
         return self._project(out, residual, None)
 
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True, emit=None):

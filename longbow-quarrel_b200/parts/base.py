@@ -127,12 +127,13 @@ class KVNeed(CacheNeed):
     v_head_dim: int | None = None        # values of another size than the keys
     values: bool = True                  # False: no pool of values (a mixer whose values are a part of its keys' rows)
     keep_first: int = 0                  # with a window: the sequence's first positions that stay readable for good
+    chunk: int | None = None             # positions see only their own block of `chunk` positions (instead of a window)
 
     def make_group(self, entries, sizing):
         from ..cache.paged import PagedKVGroup
         return PagedKVGroup(entries, self.n_kv_heads, self.head_dim, self.window, sizing.n_pages, sizing.page_size,
                             sizing.max_slots, sizing.pages_per_seq, sizing.dtype, sizing.device,
-                            v_head_dim=self.v_head_dim, values=self.values, keep_first=self.keep_first)
+                            v_head_dim=self.v_head_dim, values=self.values, keep_first=self.keep_first, chunk=self.chunk)
 
 
 @dataclass(frozen=True)
@@ -144,6 +145,18 @@ class StateNeed(CacheNeed):
     def make_group(self, entries, sizing):
         from ..cache.state import StateGroup
         return StateGroup(entries, self.shape, self.dtype, sizing.max_slots, sizing.device)
+
+
+@dataclass(frozen=True)
+class SeveralNeeds(CacheNeed):
+    """A mixer that keeps more than one kind of storage for a cache entry (keys and values for one of its sides, a
+    fixed-size state for the other): each need makes its own group, and the mixer's `cache_view` is the tuple of
+    their views, in the order of `needs`."""
+    needs: tuple
+
+    def make_group(self, entries, sizing):
+        from ..cache.group import SeveralGroups
+        return SeveralGroups(entries, [need.make_group(entries, sizing) if need is not None else None for need in self.needs])
 
 
 class Mixer(Part):

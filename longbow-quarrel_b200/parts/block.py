@@ -10,12 +10,18 @@ convolution over time) filters what the mixer reads, h <- conv1(norm1(x)), with 
 steps kept as the layer's own state; and `residual_scale` m, x += m * mixer(...), x += m * ffn(...), for which
 the mixer and the feed-forward hand back their branches as float32 rows.
 
+"stream_mix": no mixer and no feed-forward; the stream is replaced by a product over the stream and the embedding's
+rows side by side, x <- W [x; e] (what a pass over repeated layers starts with).
+
 "sandwich_norm": every branch is normed on both sides, x += norm1b(mixer(norm1(x)));
 x += norm2b(ffn(norm2(x))), and a layer may have no feed-forward.  The branch's own norm,
 the addition and the norm that reads the stream next are one kernel."""
 from __future__ import annotations
 
-from ..kernels import ops
+import torch
+
+from ..kernels import linear, ops
+from ..weights.spec import WeightSpec
 from .base import Part, Runtime, StepContext
 from .norm import RMSNorm
 from .registry import make_part, register_part
@@ -118,6 +124,11 @@ class PreNormBlock(Part):
             return self._forward_plain(x, ctx, cache_view, writes_cache, state)
         n_rows = x.shape[0]
         h = normed if normed is not None else self.norm1.forward(x)
+        if self.has_ffn and hasattr(self.mixer, "branches") and getattr(self.norm2, "takes_branches", False):
+            # A mixer of several sides: its branches join the stream in the kernel that makes the second norm's rows.
+            h = self.norm2.forward(x, add=self.mixer.branches(h, ctx, cache_view, writes_cache))
+            self.ffn.forward(h, ctx, x)
+            return None
         if not self.has_ffn:
             if emit is not None and self.mixer.folds_norm:
                 return self.mixer.forward(h, ctx, cache_view, x, writes_cache, emit=emit)
@@ -212,3 +223,34 @@ class SandwichNormBlock(Part):
         h = ops.rmsnorm_add(y, self.norm1b.gain, self.norm1b.eps, x, (self.norm2.gain, self.norm2.eps), act)
         y = self.ffn.forward(h, ctx, None)
         return ops.rmsnorm_add(y, self.norm2b.gain, self.norm2b.eps, x, emit, act)
+
+
+@register_part("block", "stream_mix")
+class StreamMixBlock(Part):
+    """x <- W [x; e]: W [D, 2 D], x the stream, e the embedding's output for the same rows.  The product reads both in
+    the model's precision and leaves the new stream in 32-bit.  It keeps nothing in the cache."""
+    graph_safe = True
+    folds_norm = False
+    replaces_stream = True       # forward returns the new stream instead of changing x in place
+    reads_embedding = True       # forward is given the embedding's rows as `embedded`
+
+    def __init__(self, runtime: Runtime, layer: LayerSpec, hidden_size: int, name: str = "in"):
+        if layer.parts:
+            raise ValueError(f"layer {layer.prefix!r}: the arrangement 'stream_mix' has no places for parts")
+        self.prefix, self.runtime, self.D, self.name = layer.prefix, runtime, int(hidden_size), name
+        self.w: linear.LinearWeight | None = None
+
+    def parts(self):
+        return ()
+
+    def cache_need(self):
+        return None
+
+    def weights(self):
+        return {self.name: WeightSpec((self.D, 2 * self.D))}
+
+    def load(self, tensors):
+        self.w = linear.LinearWeight(tensors[self.name])
+
+    def forward(self, x, ctx: StepContext, embedded):
+        return linear.linear(ops.side_by_side(x, embedded, self.runtime.act_dtype), self.w, torch.float32)

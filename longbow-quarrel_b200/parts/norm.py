@@ -40,3 +40,30 @@ class RMSNorm(Norm):
         if self.gain is None or not linear.can_defer_norm(n_rows, self.size, self.runtime.act_dtype):
             return None
         return self.gain, self.eps
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * gain + bias, var the mean of the squared deviations, in 32-bit.  The
+    bias tensor is named `bias_name` (default: the gain's name with ".b" behind it)."""
+    graph_safe = True
+
+    def __init__(self, runtime: Runtime, size: int, eps: float, name: str = "weight", bias_name: str | None = None):
+        self.runtime, self.size, self.eps, self.name = runtime, size, float(eps), name
+        self.bias_name = bias_name if bias_name is not None else name + ".b"
+        self.gain: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def weights(self):
+        return {self.name: WeightSpec((self.size,), init="gain", full_precision=True),
+                self.bias_name: WeightSpec((self.size,), init="small", full_precision=True)}
+
+    def load(self, tensors):
+        self.gain = tensors[self.name].to(torch.float32).contiguous()
+        self.bias = tensors[self.bias_name].to(torch.float32).contiguous()
+
+    def forward(self, x, rows=None, add=()):
+        """add: ((y, m), ...) branches that join the stream (x += m * y, in place) in the same pass."""
+        return ops.layernorm(x, self.gain, self.bias, self.eps, self.runtime.act_dtype, rows, add=add)
+
+    takes_branches = True       # forward(add=...) adds a mixer's branches as it norms

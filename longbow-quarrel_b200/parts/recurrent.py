@@ -21,6 +21,11 @@ fixed-size state of the sequence's slot, which is zero when a sequence starts:
              scale.  Output: all heads together over their root mean square, times a weight, times
              sigmoid(W_g h), then W_o.
 
+"channel_decay"  a_t is a vector over the key channels, S_t = diag(a_t) S_(t-1) + k_t v_t^T (the rows of S that belong
+             to a key channel decay by that channel's a_t), a_t = sigmoid(W_a2 (W_a1 h) + b)^(1/tau) through two small
+             32-bit products and the logarithm of the sigmoid; q scaled by dim^-1/2, b_t = 1.  Output: each head over
+             its root mean square, times a weight of the head's size that all heads share, times silu(W_g h), then W_o.
+
 Gates, decays, the state and the per-head norms are 32-bit in both precisions; the
 gates' pre-activations come from a 32-bit product of their own.  A sequence's tokens
 are walked in order from the state in its slot (`csrc/recurrent.cu`: one kernel for
@@ -178,4 +183,48 @@ class MLSTM(_MatrixStateMixer):
         g_off = 2 * H * dk + H * dv
         out = ops.head_norm_gate(raw, dv, self.eps, self.runtime.act_dtype, exp_neg_m=enm, weight=self.head_weight,
                                  gate=rows[:, g_off:g_off + H * dv], act="sigmoid")
+        return self._finish(out, residual)
+
+
+@register_part("mixer", "channel_decay")
+class ChannelDecay(_MatrixStateMixer):
+    def __init__(self, runtime: Runtime, hidden_size: int, n_heads: int, key_dim: int, value_dim: int, tau: float,
+                 eps: float, rank: int | None = None, names: dict | None = None):
+        """rank: the inner size of the decays' two products; None: whatever the stored tensors have."""
+        super().__init__(runtime, hidden_size, n_heads, key_dim, value_dim, eps,
+                         {"norm": "norm", "a1": "a1", "a2": "a2", "a2_bias": "a2.b", **(names or {})})
+        if not tau > 0 or (rank is not None and rank < 1):
+            raise ValueError(f"channel_decay: tau {tau} must be positive and the rank {rank} at least 1")
+        self.tau, self.rank = float(tau), int(rank) if rank is not None else -1
+        self.w_a1 = self.w_a2 = self.b_a2 = self.head_weight = None
+
+    def cache_need(self):
+        return StateNeed((self.H, self.dk, self.dv), torch.float32)
+
+    def weights(self):
+        n, H = self.names, self.H
+        return {**self._base_weights(),
+                n["norm"]: WeightSpec((self.dv,), init="gain", full_precision=True),
+                n["a1"]: WeightSpec((self.rank, self.D)), n["a2"]: WeightSpec((H * self.dk, self.rank)),
+                n["a2_bias"]: WeightSpec((H * self.dk,), init=("uniform", 0.0, 4.0), full_precision=True)}
+
+    def load(self, tensors):
+        self._load_base(tensors)
+        n = self.names
+        self.w_a1, self.w_a2 = tensors[n["a1"]].contiguous(), tensors[n["a2"]].contiguous()
+        if self.w_a1.shape[0] != self.w_a2.shape[1]:
+            raise ValueError(f"channel_decay: {n['a1']} has {self.w_a1.shape[0]} rows, {n['a2']} {self.w_a2.shape[1]} columns")
+        self.b_a2 = tensors[n["a2_bias"]].to(torch.float32).contiguous()
+        self.head_weight = tensors[n["norm"]].to(torch.float32).repeat(self.H).contiguous()     # one weight for every head
+
+    def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True):
+        H, dk, dv = self.H, self.dk, self.dv
+        rows = linear.linear(h, self.w_in, self.runtime.act_dtype)
+        # The decays enter the recurrence: their pre-activations come from 32-bit products of their own.
+        pre = ops.small_proj(ops.small_proj(h, self.w_a1), self.w_a2)
+        raw, _ = ops.linear_scan(rows, 0, H * dk, 2 * H * dk, cache_view, ctx.cu_rows, ctx.slots, ctx.tok_pos, ctx.B,
+                                 H, dk, dv, q_scale=dk ** -0.5, channel_decay=(pre, self.b_a2, self.tau), single=ctx.decode)
+        g_off = 2 * H * dk + H * dv
+        out = ops.head_norm_gate(raw, dv, self.eps, self.runtime.act_dtype, weight=self.head_weight,
+                                 gate=rows[:, g_off:g_off + H * dv], act="silu")
         return self._finish(out, residual)

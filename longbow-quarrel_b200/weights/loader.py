@@ -59,6 +59,11 @@ def _open_files(folder: Path) -> list[SafetensorsFile]:
     raise SafetensorsError(f"{folder}: neither model.safetensors nor model.safetensors.index.json")
 
 
+def _fits(stored: tuple, wanted: tuple) -> bool:
+    """Whether a stored shape is the wanted one; a wanted dimension of -1 takes any size from 1 on."""
+    return len(stored) == len(wanted) and all(s == w or (w == -1 and s >= 1) for s, w in zip(stored, wanted))
+
+
 def _keep_dtype(t: torch.Tensor, spec: WeightSpec, convert_to: torch.dtype | None = None) -> torch.Tensor:
     if spec.integer:
         return t.to(torch.int32)
@@ -135,7 +140,7 @@ def load_weights(folder, table: dict[str, WeightSpec], device, convert_to: torch
             if spec.fallback is not None and spec.fallback in table:
                 continue
             missing.append(name)
-        elif where[name].shape(name) != tuple(spec.shape):
+        elif not _fits(where[name].shape(name), tuple(spec.shape)):
             wrong.append((name, tuple(spec.shape), where[name].shape(name)))
         elif spec.integer == where[name].dtype(name).is_floating_point:
             other.append(f"tensor {name} has dtype {where[name].dtype(name)}, expected "

@@ -24,6 +24,9 @@ def tensor_seed(seed: int, name: str) -> int:
 
 def random_tensor(name: str, spec: WeightSpec, seed: int, dtype: torch.dtype, device="cpu",
                   std: float = 0.02, gain_std: float = 0.1) -> torch.Tensor:
+    if any(d < 0 for d in spec.shape):
+        raise ValueError(f"tensor {name}: the shape {tuple(spec.shape)} leaves a size open; random weights need it "
+                         f"(give the part that size)")
     gen = torch.Generator(device=device)
     gen.manual_seed(tensor_seed(seed, name))
     if spec.integer:

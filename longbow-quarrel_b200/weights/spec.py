@@ -8,7 +8,8 @@ from dataclasses import dataclass
 class WeightSpec:
     """One tensor a part reads from the checkpoint.
 
-    shape     the exact shape it must have.
+    shape     the exact shape it must have; a dimension given as -1 may have any size (a size that no key of the
+              configuration gives: the part reads it from the tensor when it loads it).
     init      how the random-weights mode fills it: "normal" (N(0, std)), "gain"
               (1 + N(0, gain_std)), "small" (N(0, gain_std): offsets of gains from one, biases), or
               ("uniform", lo, hi).
