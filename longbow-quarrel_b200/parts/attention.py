@@ -68,10 +68,10 @@ class Attention(Mixer):
                  q_temp: tuple | None = None, chunk: int | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
-        if head_dim % 2 or not 2 <= head_dim <= 256:
+        if (head_dim % 2 and position is not None) or not 1 <= head_dim <= 256:
             # Pairs of the rotation need an even size; the plain kernels hold a head in 256 threads' registers.
             # Which of the faster kernels take a head size is each kernel's own rule (kernels/attention.py).
-            raise ValueError(f"attention: head_dim {head_dim} must be even and at most 256")
+            raise ValueError(f"attention: head_dim {head_dim} must be at most 256, and even where it is rotated")
         self.runtime = runtime
         self.D, self.H, self.Hkv, self.hd = hidden_size, n_heads, n_kv_heads, head_dim
         self.scale, self.window, self.own_kv = float(scale), window, own_kv
