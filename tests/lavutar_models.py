@@ -206,7 +206,7 @@ def load(folder):
     return json.loads((Path(folder) / "config.json").read_text()), plain_lavutar.read_safetensors(Path(folder) / "model.safetensors")
 
 
-CLOSE_CALL = 0.05      # in router logits: rounding in bfloat16 moves a router's logits by less
+CLOSE_CALL = 0.02      # in router logits: rounding in bfloat16 moves a router's logits by less
 
 
 def firm_rows(dtype: str, cfg: dict, weights: dict, toks) -> np.ndarray:
@@ -218,6 +218,12 @@ def firm_rows(dtype: str, cfg: dict, weights: dict, toks) -> np.ndarray:
         margins: list = []
         plain_lavutar.forward(cfg, weights, toks, margins=margins)
         per_layer = np.asarray(margins, dtype=np.float64).reshape(-1, len(toks)) if margins else np.zeros((0, len(toks)))
+        # The other row is a key and a value for the positions after it: where a window or a block is short it weighs as
+        # much as a fifth of what they see, so the rows within reach of a close call through such a layer are left out as
+        # well (through longer windows and blocks it is one key among many).
+        spans = [m.get("mask", {}).get("size") for layer in cfg["layers"] for m in [layer["mixer"]] if isinstance(m.get("mask"), dict)]
+        reach = max([s for s in spans if s < 16], default=0)
         for m in per_layer:
-            firm &= m >= CLOSE_CALL
+            for p in np.nonzero(m < CLOSE_CALL)[0]:
+                firm[p:p + reach + 1] = False
     return firm

@@ -238,7 +238,10 @@ def test_plain_attention_over_blocks_with_a_sink_and_a_gate_per_head(dtype, H, G
                               case.page, scale, None, vd=vd, softcap=cap, chunk=block, sink=sink, gate=gate, gate_per_head=True)
     ref = case.reference(q[:, :H * hd].reshape(-1, H, hd), tok_seq, tok_pos, H, scale, block, cap, sink)
     ref = ref * torch.sigmoid(gate.double().cpu())[:, :, None]
-    _close(out.reshape(-1, H, vd), ref, 3e-6 if dtype == torch.float32 else 1e-2)
+    if dtype == torch.float32:
+        _close(out.reshape(-1, H, vd), ref, 3e-6)
+    else:
+        _close(out.reshape(-1, H, vd), ref, 1e-2, BF16_ULP)      # beyond the rounding of each output to bfloat16
 
 
 # H, G, hd, block, cap: what the tensor-core kernels take (values as wide as keys)
@@ -347,7 +350,7 @@ def test_one_key_that_outweighs_all_others_shows_the_blocks_edges(kernel, block)
     case = Pages([n], 1, hd, hd, torch.bfloat16, seed=7, poison=3.0e38 if kernel == "tc" else float("nan"))
     q = _rand((n, hd), torch.bfloat16, 75)
     if block == 150:
-        plants = {(150, 299): True, (149, 290): False, (300, 459): True, (299, 301): False, (0, 149): True, (300, 300): True}
+        plants = {(150, 299): True, (149, 290): False, (450, 459): True, (449, 451): False, (0, 149): True, (300, 300): True, (299, 310): False}
     else:
         plants = {(3, 459): True, (0, 200): True, (390, 391): True}
     for (key_pos, row) in plants:
