@@ -398,6 +398,8 @@ def design_bench(args) -> int:
         return zoporax_bench(args)
     if args.design == "raritar":
         return raritar_bench(args)
+    if args.design == "lavutar":
+        return lavutar_bench(args)
     return fetorax_bench(args)
 
 
@@ -661,6 +663,132 @@ def raritar_bench(args) -> int:
     return 0
 
 
+def lavutar_config(size: str, block: int, window: int) -> dict:
+    """Four layers: attention over blocks of positions with whole-projection norms, capped scores and a gate per head,
+    behind a gated feed-forward; two sides side by side (softmax attention with per-head norms and a query temperature,
+    linear attention with a decay for every key channel) behind routed gated experts; windowed attention with a
+    YaRN-blended rotation behind a gated feed-forward; the two sides again behind a gated feed-forward.  The middle two
+    layers are a stretch that is entered through the product over the stream and the embedding's rows."""
+    width, heads, kv, dim, ff = DESIGN_SIZES[size]
+    experts, top, eff = ZOPORAX_SIZES[size][8:11]
+    dense = {"kind": "dense", "ff": ff}
+    soft = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5}
+    two = {"left": dict(soft, q_temp={"coef": 0.1, "every": 256}), "left_scale": 0.8, "right_scale": 0.5,
+           "right": {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": 64}}
+    layers = [
+        {"type": "attention_2", "mixer": dict(soft, softcap=50.0, mask={"size": block}), "mlp": dense},
+        {"type": "parallel", "mixer": two, "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top}}},
+        {"type": "attention", "mixer": dict(soft, mask={"size": window}, rot={"dims": dim, "base": 5e4, "scaling": {
+            "factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}), "mlp": dense},
+        {"type": "parallel", "mixer": two, "mlp": dense}]
+    return {"architecture": "Lavutar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "layers": layers,
+            "loop": {"start": 1, "stop": 3, "times": 1}, "max_positions": 8192}
+
+
+def lavutar_bench(args) -> int:
+    """Prefill and decode of a Lavutar model of realistic layer sizes beside the closest model the library has, a
+    Fetorax model of attention (sink and gate) and retention layers of the same width, depth and feed-forward width
+    (random weights, vocabulary 32,000): tokens a second, what every kind of kernel adds to a prompt step and to a decode
+    step, and for the design's kernels how many times their roofline they take, beside the like kernel of the other model."""
+    import numpy as np
+    import torch
+
+    from longbow_quarrel_b200.engine import Engine
+    peaks, peaks_from = load_peaks()
+    K, W = args.steps, max(3, args.warmup)
+    T, B, ctx = PREFILL_TOKENS, BATCH, 2048
+    hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {}
+    for size in args.sizes.split(","):
+        width, heads, kv, dim, ff = DESIGN_SIZES[size]
+        experts, top, eff = ZOPORAX_SIZES[size][8:11]
+        beside = fetorax_config(width, heads, kv, dim, ff)
+        for i, layer in enumerate(beside["layers"]):       # attention and retention by turns, each with keys of its own
+            if i % 2:
+                layer["type"], layer["mixer"] = "retention", dict(beside["layers"][1]["mixer"])
+            else:
+                layer["type"], layer["mixer"] = "attention", {k: v for k, v in beside["layers"][0]["mixer"].items() if k != "kv_from"}
+        block, window = 1024, 1024
+        configs = {"lavutar": lavutar_config(size, block, window), "fetorax": beside}
+        res = {name: _design_run(torch, np, Engine, cfg, name, T, B, ctx, K, W, rng) for name, cfg in configs.items()}
+
+        def per_launch(kinds, *names):
+            n = sum(kinds[k][0] for k in names if k in kinds)
+            return sum(kinds[k][1] for k in names if k in kinds) / n if n else None
+
+        def times(us, nbytes, flops):
+            return round(us / (max(nbytes / hbm, flops / tensor) * 1e6), 2) if us else None
+
+        def us(kinds, *names):
+            v = per_launch(kinds, *names)
+            return round(v, 1) if v is not None else None
+        v, f = res["lavutar"], res["fetorax"]
+        vp, vd, fp, fd = v["prefill_kernels_us"], v["decode_kernels_us"], f["prefill_kernels_us"], f["decode_kernels_us"]
+        qkv_bytes = T * heads * 3 * dim * 2.0
+        # Visible (query, key) pairs of a prompt: all earlier positions; a window or blocks of 1,024 positions see about
+        # three quarters of them at 2,048 tokens.  The design's three attentions share one kernel: their mean is taken.
+        full = T * (T + 1) / 2
+        seen = (full + (full - (T - window) * (T - window + 1) / 2) + 2 * (block * (block + 1) / 2) + full) / 4 if T > window else full
+        scan_bytes = qkv_bytes + T * heads * dim * 4.0
+        scan_flops = 4.0 * T * heads * dim * dim
+        state = B * heads * dim * dim * 4.0 * 2
+        kv_read = B * ctx * 2 * kv * dim * 2.0
+        kv_seen = B * (ctx + min(ctx, window) + (ctx % block + 1) + ctx) / 4 * 2 * kv * dim * 2.0
+        roof = {
+            "prefill": {
+                "fetorax attention (sink, gate)": times(per_launch(fp, "attn_prefill_two", "attn_prefill_tc", "attn_prefill"),
+                                                        qkv_bytes, 4.0 * heads * dim * full),
+                "lavutar attention (blocks / window / all, sink)": times(per_launch(vp, "attn_prefill_two", "attn_prefill_tc", "attn_prefill"),
+                                                                         qkv_bytes, 4.0 * heads * dim * seen),
+                "fetorax recurrent scan": times(per_launch(fp, "linear_scan"), scan_bytes, scan_flops),
+                "lavutar recurrent scan (channel decays)": times(per_launch(vp, "linear_scan"), scan_bytes + T * heads * dim * 4.0, scan_flops),
+                "fetorax norm": times(per_launch(fp, "rmsnorm_add", "rmsnorm", "rmsnorm_vec"), T * width * 10.0, 0.0),
+                # Seven of its nine launches norm the stream alone (4 bytes in, 2 out a number); two also add both sides'
+                # branches into it (8 for the stream, 8 for the branches, 2 out).
+                "lavutar layer norm": times(per_launch(vp, "layernorm", "layernorm_vec"), T * width * (7 * 6.0 + 2 * 18.0) / 9, 0.0),
+                "fetorax rotation + cache write": times(per_launch(fp, "rope_partial"), T * (heads + 2 * kv) * dim * 6.0, 0.0),
+                "lavutar unit norms + rotation + cache write": times(per_launch(vp, "rope_partial"), T * (heads + 2 * kv) * dim * 6.0, 0.0),
+                "lavutar experts, either product": times(sum(vp.get(k, (0, 0.0))[1] for k in ("gemm_tc_grouped", "gemm_tc")) / 2 or None,
+                                                         experts * eff * width * 2.0 * 1.5, 2.0 * T * top * eff * width * 1.5),
+            },
+            "decode": {
+                "fetorax attention (sink, gate)": times(per_launch(fd, "attn_decode"), kv_read, 0.0),
+                "lavutar attention (blocks / window / all, sink)": times(per_launch(vd, "attn_decode"), kv_seen, 0.0),
+                "fetorax recurrent scan": times(per_launch(fd, "linear_scan_single"), state, 0.0),
+                "lavutar recurrent scan (channel decays)": times(per_launch(vd, "linear_scan_single"), state, 0.0),
+                "lavutar experts, first product": times(per_launch(vd, "moe_up", "moe_up_rows"), min(B * top, experts) * eff * width * 4.0, 0.0),
+                "lavutar experts, second product": times(per_launch(vd, "moe_down"), min(B * top, experts) * eff * width * 2.0, 0.0),
+            },
+        }
+        small = {"prefill_us_per_launch": {k: us(vp, *names) for k, names in {
+                     "layer norm": ("layernorm", "layernorm_vec"), "unit norms + rotation + cache write": ("rope_partial",),
+                     "stream and embedding side by side": ("side_by_side", "side_by_side_vec"), "gate after attention": ("gate_mul",),
+                     "gelu(gate) * up": ("gated_act", "gated_act_vec"), "decays' second product (32-bit)": ("gemm_plain",), "unit norm per head + gate": ("head_norm_gate", "head_norm_gate_wide"),
+                     "router's 32-bit product": ("small_proj",), "router choice": ("moe_route",)}.items()},
+                 "decode_us_per_launch": {k: us(vd, *names) for k, names in {
+                     "layer norm": ("layernorm", "layernorm_vec"), "unit norms + rotation + cache write": ("rope_partial",),
+                     "gate after attention": ("gate_mul",), "gelu(gate) * up": ("gated_act", "gated_act_vec"),
+                     "decays' second product (32-bit)": ("gemm_plain",),
+                     "unit norm per head + gate": ("head_norm_gate", "head_norm_gate_wide"),
+                     "router's 32-bit product": ("small_proj",)}.items()},
+                 "fetorax_prefill_us_per_launch": {k: us(fp, *names) for k, names in {
+                     "branch norm + add + next norm": ("rmsnorm_add",), "biases + rotation + cache write": ("rope_partial",),
+                     "gate after attention": ("gate_mul",), "unit norm per head + gate": ("head_norm_gate",)}.items()}}
+        out[size] = {"lavutar": v, "fetorax": f, "times_the_roofline": roof, "small_kernels": small,
+                     "lavutar_over_fetorax": {"prefill": round(v["prefill_tokens_per_s"] / f["prefill_tokens_per_s"], 3),
+                                              "decode": round(v["decode_tokens_per_s"] / f["decode_tokens_per_s"], 3)}}
+    clocks = sampler.stop()
+    print(json.dumps({"design": "lavutar", "beside": "fetorax", "dtype": "bf16", "data": "synthetic", "layers": 4,
+                      "layer_order": "attention over blocks + gated ff, two sides + experts, windowed attention + gated ff, two sides + gated ff "
+                                     "(the middle two behind the stream's product); beside attention, retention, attention, retention, each + ff",
+                      "vocab": DESIGN_VOCAB, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx, "steps": K,
+                      "warmup": W, "peaks": peaks, "peaks_from": peaks_from, "clocks": clocks, "sizes": out}))
+    return 0
+
+
 def fetorax_bench(args) -> int:
     """Prefill and decode of a Fetorax model of the 1B and 8B layer sizes beside a Llama model of the same sizes
     (random weights, vocabulary cut to 32,000): tokens a second, the device time of every kind of kernel in one
@@ -770,9 +898,9 @@ def fetorax_bench(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default="", choices=["", "fetorax", "zoporax", "raritar"],
+    ap.add_argument("--design", default="", choices=["", "fetorax", "zoporax", "raritar", "lavutar"],
                     help="instead of the default workload: this design beside the closest model the library has, at equal layer "
-                         "sizes (prefill, decode, kernel by kernel): fetorax beside Llama, zoporax beside Fetorax, raritar beside Llama")
+                         "sizes (prefill, decode, kernel by kernel): fetorax beside Llama, zoporax beside Fetorax, raritar beside Llama, lavutar beside Fetorax")
     ap.add_argument("--sizes", default="1b,8b", help="--design: layer sizes to run, of " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)

@@ -408,10 +408,99 @@ layernorm_kernel(float* __restrict__ x, const float* __restrict__ y1, float m1, 
         out[(size_t)r * D + i] = from_f32<TO>((xr[i] - mean) * inv * gain[i] + (bias ? bias[i] : 0.f));
 }
 
+// Rows whose length is a multiple of 4 and at most 256 * 4 * RMS_VEC: each thread keeps its part of the row in registers
+// (one read of the stream and of the branches), float4 loads, packed stores; the same two passes over the registers.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y1, float m1, const float* __restrict__ y2, float m2,
+                     const float* __restrict__ gain, const float* __restrict__ bias, const int* __restrict__ rows,
+                     TO* __restrict__ out, int D, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float partial[8];
+    __shared__ float stat;
+    const int r = blockIdx.x, tid = threadIdx.x, n4 = D >> 2;
+    const size_t at = (size_t)(rows ? rows[r] : r) * D;
+    float4* xr = reinterpret_cast<float4*>(x + at);
+    float4 v[RMS_VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int c = tid + i * 256;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < n4) {
+            v[i] = xr[c];
+            if (y1) {
+                const float4 a = reinterpret_cast<const float4*>(y1 + at)[c];
+                v[i].x = fmaf(m1, a.x, v[i].x); v[i].y = fmaf(m1, a.y, v[i].y); v[i].z = fmaf(m1, a.z, v[i].z); v[i].w = fmaf(m1, a.w, v[i].w);
+                if (y2) {
+                    const float4 b = reinterpret_cast<const float4*>(y2 + at)[c];
+                    v[i].x = fmaf(m2, b.x, v[i].x); v[i].y = fmaf(m2, b.y, v[i].y); v[i].z = fmaf(m2, b.z, v[i].z); v[i].w = fmaf(m2, b.w, v[i].w);
+                }
+                xr[c] = v[i];
+            }
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+    }
+    s = warp_sum(s);
+    if ((tid & 31) == 0) partial[tid >> 5] = s;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        stat = t / (float)D;
+    }
+    __syncthreads();
+    const float mean = stat;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        if (tid + i * 256 < n4) {
+            v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+            q = fmaf(v[i].x, v[i].x, q); q = fmaf(v[i].y, v[i].y, q); q = fmaf(v[i].z, v[i].z, q); q = fmaf(v[i].w, v[i].w, q);
+        }
+    }
+    q = warp_sum(q);
+    __syncthreads();
+    if ((tid & 31) == 0) partial[tid >> 5] = q;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += partial[w];
+        stat = 1.0f / sqrtf(t / (float)D + eps);
+    }
+    __syncthreads();
+    const float inv = stat;
+    const float4* g4 = reinterpret_cast<const float4*>(gain);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int c = tid + i * 256;
+        if (c >= n4) break;
+        const float4 g = g4[c], b = bias ? b4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float o0 = fmaf(v[i].x * inv, g.x, b.x), o1 = fmaf(v[i].y * inv, g.y, b.y);
+        const float o2 = fmaf(v[i].z * inv, g.z, b.z), o3 = fmaf(v[i].w * inv, g.w, b.w);
+        if (sizeof(TO) == 4) {
+            reinterpret_cast<float4*>(out + (size_t)r * D)[c] = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+            reinterpret_cast<uint2*>(out + (size_t)r * D)[c] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+    }
+}
+
 LQ_EXPORT int lq_layernorm(float* x, const float* y1, float m1, const float* y2, float m2, const float* gain, const float* bias,
                            const int* rows, void* out, int out_dtype, int n_rows, int D, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return LQ_OK;
     if ((rows && y1) || (y2 && !y1)) return LQ_BAD_SIZE;
+    const bool vec = D % 4 == 0 && D <= 256 * 4 * RMS_VEC &&
+        (((uintptr_t)x | (uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)gain | (uintptr_t)bias | (uintptr_t)out) & 15) == 0;
+    if (vec && out_dtype == LQ_F32)
+        return launch_pdl(layernorm_vec_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, y1, m1, y2, m2, gain, bias, rows,
+                          (float*)out, D, eps);
+    if (vec && out_dtype == LQ_BF16)
+        return launch_pdl(layernorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, x, y1, m1, y2, m2, gain, bias, rows,
+                          (__nv_bfloat16*)out, D, eps);
     if (out_dtype == LQ_F32)
         return launch_pdl(layernorm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, x, y1, m1, y2, m2, gain, bias, rows,
                           (float*)out, D, eps);
@@ -436,9 +525,36 @@ __global__ void side_by_side_kernel(const float* __restrict__ a, const float* __
     out[i] = from_f32<TO>(c < D ? a[t * D + c] : b[t * D + c - D]);
 }
 
+// Four columns a thread (D a multiple of 4, 16-byte aligned tensors).
+template <typename TO>
+__global__ void side_by_side_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b, TO* __restrict__ out, int D4,
+                                        size_t total4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const size_t t = i / (2 * D4);
+    const int c = (int)(i % (2 * D4));
+    const float4 v = c < D4 ? a[t * D4 + c] : b[t * D4 + c - D4];
+    if (sizeof(TO) == 4) {
+        reinterpret_cast<float4*>(out)[i] = v;
+    } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+}
+
 LQ_EXPORT int lq_side_by_side(const float* a, const float* b, void* out, int out_dtype, int T, int D, cudaStream_t stream) {
     const size_t total = (size_t)T * 2 * D;
     if (total == 0) return LQ_OK;
+    if (D % 4 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0 && (out_dtype == LQ_F32 || out_dtype == LQ_BF16)) {
+        const unsigned blocks4 = (unsigned)((total / 4 + 255) / 256);
+        if (out_dtype == LQ_F32)
+            return launch_pdl(side_by_side_vec_kernel<float>, dim3(blocks4), dim3(256), 0, stream, (const float4*)a, (const float4*)b,
+                              (float*)out, D / 4, total / 4);
+        return launch_pdl(side_by_side_vec_kernel<__nv_bfloat16>, dim3(blocks4), dim3(256), 0, stream, (const float4*)a, (const float4*)b,
+                          (__nv_bfloat16*)out, D / 4, total / 4);
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dtype == LQ_F32)
         return launch_pdl(side_by_side_kernel<float>, dim3(blocks), dim3(256), 0, stream, a, b, (float*)out, D, total);
@@ -1058,11 +1174,40 @@ __global__ void gated_act_kernel(const TI* __restrict__ gu, const float* __restr
     out[i] = from_f32<TO>(activation(g, act) * u);
 }
 
+// bfloat16 in and out, F a multiple of 8: eight outputs a thread from two 16-byte loads, the same arithmetic.
+__global__ void gated_act_vec_kernel(const uint4* __restrict__ gu, const float* __restrict__ bias, uint4* __restrict__ out,
+                                     size_t total8, int F8, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const size_t t = i / F8;
+    const int f8 = (int)(i % F8);
+    uint4 g = gu[t * 2 * F8 + f8], u = gu[t * 2 * F8 + F8 + f8], o;
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float2 gv = __bfloat1622float2(gp[j]), uv = __bfloat1622float2(up[j]);
+        if (bias) {
+            const int f = f8 * 8 + 2 * j;
+            gv.x += bias[f]; gv.y += bias[f + 1];
+            uv.x += bias[8 * F8 + f]; uv.y += bias[8 * F8 + f + 1];
+        }
+        op[j] = __floats2bfloat162_rn(activation(gv.x, act) * uv.x, activation(gv.y, act) * uv.y);
+    }
+    out[i] = o;
+}
+
 LQ_EXPORT int lq_gated_act(const void* gu, int in_dtype, const float* bias, void* out, int out_dtype, int T, int F, int act,
                            cudaStream_t stream) {
     const size_t total = (size_t)T * F;
     if (total == 0) return LQ_OK;
     if (act < 0 || act > 4) return LQ_BAD_SIZE;
+    if (in_dtype == LQ_BF16 && out_dtype == LQ_BF16 && F % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0)
+        return launch_pdl(gated_act_vec_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream, (const uint4*)gu, bias,
+                          (uint4*)out, total / 8, F / 8, act);
     const unsigned blocks = (unsigned)((total + 255) / 256);
     typedef __nv_bfloat16 bf;
     if (in_dtype == LQ_F32 && out_dtype == LQ_F32)

@@ -211,17 +211,19 @@ class ChannelDecay(_MatrixStateMixer):
     def load(self, tensors):
         self._load_base(tensors)
         n = self.names
-        self.w_a1, self.w_a2 = tensors[n["a1"]].contiguous(), tensors[n["a2"]].contiguous()
-        if self.w_a1.shape[0] != self.w_a2.shape[1]:
-            raise ValueError(f"channel_decay: {n['a1']} has {self.w_a1.shape[0]} rows, {n['a2']} {self.w_a2.shape[1]} columns")
+        self.w_a1, self.w_a2 = linear.LinearWeight(tensors[n["a1"]]), tensors[n["a2"]].contiguous()
+        if self.w_a1.N != self.w_a2.shape[1]:
+            raise ValueError(f"channel_decay: {n['a1']} has {self.w_a1.N} rows, {n['a2']} {self.w_a2.shape[1]} columns")
         self.b_a2 = tensors[n["a2_bias"]].to(torch.float32).contiguous()
         self.head_weight = tensors[n["norm"]].to(torch.float32).repeat(self.H).contiguous()     # one weight for every head
 
     def forward(self, h, ctx: StepContext, cache_view, residual, writes_cache: bool = True):
         H, dk, dv = self.H, self.dk, self.dv
         rows = linear.linear(h, self.w_in, self.runtime.act_dtype)
-        # The decays enter the recurrence: their pre-activations come from 32-bit products of their own.
-        pre = ops.small_proj(ops.small_proj(h, self.w_a1), self.w_a2)
+        # The decays enter the recurrence: the first of their two products (over the layer's width) runs as the layer's
+        # other products do and hands on its 32-bit sums unrounded; the second (over the small inner size) is a 32-bit
+        # product, so that nothing between the first product's sums and the decay itself is rounded.
+        pre = ops.gemm_plain(linear.linear(h, self.w_a1, torch.float32), self.w_a2, torch.float32)
         raw, _ = ops.linear_scan(rows, 0, H * dk, 2 * H * dk, cache_view, ctx.cu_rows, ctx.slots, ctx.tok_pos, ctx.B,
                                  H, dk, dv, q_scale=dk ** -0.5, channel_decay=(pre, self.b_a2, self.tau), single=ctx.decode)
         g_off = 2 * H * dk + H * dv
