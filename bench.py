@@ -416,12 +416,16 @@ def _design_run(torch, np, Engine, cfg, name, T, B, ctx, K, W, rng) -> dict:
     for _ in range(W):
         prefill()
     a, b = events(torch)
+    fast = FastClocks()              # the SM clock inside the two timed regions (the run's median also holds the idle set-up)
+    fast.start()
     torch.cuda.synchronize()
+    t_pre = [time.perf_counter()]
     a.record()
     for _ in range(max(3, K // 4)):
         prefill()
     b.record()
     torch.cuda.synchronize()
+    t_pre.append(time.perf_counter())
     prefill_ms = a.elapsed_time(b) / max(3, K // 4)
     prefill_kinds, _ = _kernel_times(torch, prefill)
     slots = [eng.new_sequence() for _ in range(B)]
@@ -435,14 +439,18 @@ def _design_run(torch, np, Engine, cfg, name, T, B, ctx, K, W, rng) -> dict:
     for _ in range(W):
         decode()
     torch.cuda.synchronize()
+    t_dec = [time.perf_counter()]
     a.record()
     for _ in range(K):
         decode()
     b.record()
     torch.cuda.synchronize()
+    t_dec.append(time.perf_counter())
+    fast.stop()
     decode_ms = a.elapsed_time(b) / K
     decode_kinds, _ = _kernel_times(torch, decode)
-    res = {"prefill_tokens_per_s": round(T / prefill_ms * 1e3), "prefill_ms": round(prefill_ms, 3),
+    res = {"sm_mhz_timed": {"prefill": fast.median_between(*t_pre), "decode": fast.median_between(*t_dec)},
+           "prefill_tokens_per_s": round(T / prefill_ms * 1e3), "prefill_ms": round(prefill_ms, 3),
            "decode_tokens_per_s": round(B / decode_ms * 1e3), "decode_ms_per_step": round(decode_ms, 4),
            "prefill_kernels_us": prefill_kinds, "decode_kernels_us": decode_kinds, "weight_bytes": eng.model.weight_bytes()}
     eng.close()
