@@ -364,6 +364,35 @@ def test_one_key_that_outweighs_all_others_shows_the_blocks_edges(kernel, block)
     _close(out.reshape(n, 1, hd), ref, 2 * case.tol(ref), BF16_ULP)
 
 
+@pytest.mark.parametrize("kernel", ["plain", "decode", "mma", "tc"])
+def test_a_sink_that_outweighs_every_key_empties_the_head(kernel):
+    """Two heads on one key head, 300 keys in blocks of 100: the first head's term in the denominator is e^30 times what its
+    keys weigh, so its output is next to nothing at every position; the second head's is e^-30 of it and changes nothing."""
+    ops = _ops()
+    hd, n, block, H = 64, 300, 100, 2
+    case = Pages([n], 1, hd, hd, torch.bfloat16, seed=9, poison=3.0e38 if kernel == "tc" else float("nan"))
+    q = _rand((n, H * hd), torch.bfloat16, 77)
+    sink = torch.tensor([30.0, -30.0], dtype=torch.float32, device=DEV)
+    args = (case.k_pages, case.v_pages, case.table)
+    mask = ops.span(None, block)
+    if kernel == "plain":
+        out = ops.attention_plain(q, *args, _i32(list(range(n))), _i32([0] * n), case.slots, H, 1, hd, 64, 0.05, None, chunk=block, sink=sink)
+    elif kernel == "decode":
+        rows = [0, 1, 99, 100, 199, 299]
+        out = torch.zeros((n, H * hd), dtype=torch.bfloat16, device=DEV)
+        for p in rows:
+            out[p] = ops.attn_decode(q[p:p + 1], *args, _i32([p]), _i32([0]), case.slots, H, 1, hd, 64, 0.05, mask, 2, sink=sink)[0]
+    elif kernel == "mma":
+        out = ops.attn_prefill(q, *args, case.slots, _i32([n]), _blocks([n], [0], 64), H, 1, hd, 64, 0.05, mask, sink=sink)
+    else:
+        out = ops.attn_prefill_tc(q, *args, case.slots, _i32([n]), _blocks([n], [0], 128), H, 1, hd, 64, 0.05, mask, sink=sink)
+    ref = case.reference(q.reshape(n, H, hd), [0] * n, list(range(n)), H, 0.05, block)          # without any sink
+    rows = [0, 1, 99, 100, 199, 299] if kernel == "decode" else list(range(n))
+    got = out.reshape(n, H, hd)[rows].float().cpu()
+    assert float(got[:, 0].abs().max()) < 1e-6                                                  # emptied
+    _close(got[:, 1], ref[rows][:, 1], 2 * case.tol(ref), BF16_ULP)                             # untouched
+
+
 # ------------------------------------------------------------------ the scan with a decay for every key channel
 
 def _scan_reference(q, k, v, pre, bias, tau, H, dk, dv, state):
