@@ -6,7 +6,8 @@
 // Scores and the weighted sum run on the tensor cores (mma.sync m16n8k16, bfloat16 in,
 // float32 out); the softmax is computed online in 32-bit: running maximum and sum per row,
 // the output rescaled when the maximum grows.  A row at position p sees keys
-// max(0, p - window + 1) .. p of its own sequence, whatever else the batch holds.
+// lq_first_key(p, window) .. p of its own sequence (the last `window` positions; with window < 0 its own block of
+// -window positions; with 0 all of them), whatever else the batch holds.
 //
 // The work list (which block serves which rows) is made on the host: sequence, first
 // packed row, number of rows, position of the first row.

@@ -25,7 +25,8 @@
 // the keys and values streamed from L2 (64 KB a tile, every block its own) come to 5.6 TB/s over all
 // SMs: the kernel is bound by that stream, not by the softmax.  Two query tiles per block that share
 // each tile of keys would halve it.
-// A row at position p sees keys max(0, p - window + 1) .. p of its own sequence.  Whole pages
+// A row at position p sees keys lq_first_key(p, window) .. p of its own sequence: the last `window` positions
+// (window > 0), its own block of -window positions (window < 0), or all of them (0).  Whole pages
 // are loaded, so rows of a page beyond a sequence's length are multiplied by probability zero:
 // the cache must hold finite values everywhere (it is zero-filled when it is made).
 // Every wait on a barrier is bounded (status word, as in gemm_tc).

@@ -1186,7 +1186,8 @@ def attn_prefill(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len, q
     """Causal attention of blocks of query rows over the paged bfloat16 cache (flash style:
     tensor-core products, online softmax in float32).  query_blocks = (sequence, first row,
     rows, first position) int32 tensors, one entry for each block of at most 64 rows.  softcap c: score <-
-    c tanh(score / c) after the scale; keep_first n (with a window): a row's first n keys stay visible."""
+    c tanh(score / c) after the scale; keep_first n (with a window): a row's first n keys stay visible.  window: as `span`
+    makes it (w positions; -n for blocks of n positions; 0 or None for all)."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_prefill takes bfloat16 queries and cache")
@@ -1212,7 +1213,7 @@ def attn_prefill_tc(q: torch.Tensor, k_pages, v_pages, page_table, slots, kv_len
                     keep_first: int = 0) -> torch.Tensor:
     """attn_prefill on the tcgen05 tensor cores (TMA-fed, S and O in tensor memory): blocks of at
     most 128 query rows, head_dim 64 or 128, pages of 64 keys, a cache that is finite everywhere.  softcap and
-    keep_first as in attn_prefill."""
+    keep_first as in attn_prefill.  window: as `span` makes it (w positions; -n for blocks of n positions; 0 or None for all)."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_tc takes bfloat16 queries and cache")
@@ -1254,7 +1255,9 @@ def attn_decode(q: torch.Tensor, k_pages, v_pages, page_table, tok_pos, tok_seq,
     written by the kernel ahead on the stream (a decode step: one new token per sequence); the kernel
     then requests the others without waiting for that kernel.  softcap c: score <- c tanh(score / c) after the
     scale.  keep_first n (with a window): a token's first n keys stay visible once its window has moved past them;
-    the tiles that a work list counts are then the kept tiles ahead of the window and after them the window's."""
+    the tiles that a work list counts are then the kept tiles ahead of the window and after them the window's.
+    window: as `span` makes it (w positions; -n for blocks of n positions, whose tiles a work list counts from the
+    block's first; 0 or None for all)."""
     T = q.shape[0]
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attn_decode takes bfloat16 queries and cache")
