@@ -686,7 +686,7 @@ def lavutar_config(size: str, block: int, window: int) -> dict:
     layers = [
         {"type": "attention_2", "mixer": dict(soft, softcap=50.0, mask={"size": block}), "mlp": dense},
         {"type": "parallel", "mixer": two, "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": experts, "top": top}}},
-        {"type": "attention", "mixer": dict(soft, mask={"size": window}, rot={"dims": dim, "base": 5e4, "scaling": {
+        {"type": "attention", "mixer": dict(soft, mask={"size": window}, rot={"dims": dim, "base": 1e5, "scaling": {
             "factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}), "mlp": dense},
         {"type": "parallel", "mixer": two, "mlp": dense}]
     return {"architecture": "Lavutar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "layers": layers,
